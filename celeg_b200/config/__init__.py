@@ -6,10 +6,13 @@ from .registry import (Architecture, architecture_named, architecture_of, known_
 from .lfm2 import CONV, FULL_ATTENTION, Lfm2Config
 from . import lfm2_arch as _lfm2_arch  # registers "lfm2"
 from .lfm2_arch import build_lfm2_spec
+from .ramosun import RamosunConfig
+from . import ramosun_arch as _ramosun_arch  # registers "Ramosun"
+from .ramosun_arch import build_ramosun_spec
 
 __all__ = [
     "Architecture", "ConfigError", "UnknownArchitectureError", "ExecutionEntry", "LayerSpec",
     "ModelSpec", "PartSpec", "TensorRef", "architecture_named", "architecture_of",
     "known_architectures", "read_config_json", "register_architecture", "CONV",
-    "FULL_ATTENTION", "Lfm2Config", "build_lfm2_spec",
+    "FULL_ATTENTION", "Lfm2Config", "build_lfm2_spec", "RamosunConfig", "build_ramosun_spec",
 ]

@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (config.json ``model_type``) to its
+"""One registry from an architecture's name (config.json ``model_type``, else ``architecture``) to its
 typed configuration and its model builder.
 
 celeg keeps an ``ArchitectureCatalog`` that is filled at start-up and then
@@ -51,8 +51,11 @@ def architecture_named(name: str) -> Architecture:
 def architecture_of(raw_config: Mapping[str, Any]) -> Architecture:
     model_type = raw_config.get("model_type")
     if not isinstance(model_type, str) or not model_type:
+        model_type = raw_config.get("architecture")       # (some designs name themselves under this key)
+    if not isinstance(model_type, str) or not model_type:
         raise UnknownArchitectureError(
-            "config.json has no 'model_type'; known: " + (", ".join(known_architectures()) or "none"))
+            "config.json has neither 'model_type' nor 'architecture'; known: "
+            + (", ".join(known_architectures()) or "none"))
     return architecture_named(model_type)
 
 

@@ -78,9 +78,12 @@ class ExecutionEntry:
     mixer uses. ``cache_of`` is the index of an EARLIER entry of the order whose
     cache this entry reads instead of owning one; ``None`` means it owns its own.
     A layer named at two positions runs twice with the same weights and, unless
-    ``cache_of`` says otherwise, two caches."""
+    ``cache_of`` says otherwise, two caches. ``before`` lets something happen between two blocks, such as the
+    projection that a repeated run of layers is entered through."""
     layer: int
     cache_of: Optional[int] = None
+    # names of the model's stream parts (``ModelSpec.stream_parts``) that run right before this position's block
+    before: Tuple[str, ...] = ()
 
 
 @dataclass(frozen=True)
@@ -105,6 +108,10 @@ class ModelSpec:
     # lists every tensor they need in them; ``embedding`` still names the table (its rows are the vocabulary).
     input: Optional[PartSpec] = None
     output: Optional[PartSpec] = None
+    # parts of the category "stream" by name: they rewrite the residual stream between two blocks, at the
+    # positions of the run order that name them in ``before``
+    stream_parts: Mapping[str, PartSpec] = field(default_factory=dict)
+    logit_softcap: Optional[float] = None     # built-in output: logits <- cap * tanh(logits / cap)
 
     def input_part(self) -> PartSpec:
         if self.input is not None:
@@ -115,7 +122,7 @@ class ModelSpec:
     def output_part(self) -> PartSpec:
         if self.output is not None:
             return self.output
-        return PartSpec("norm_head", params={"multiplier": self.logits_multiplier},
+        return PartSpec("norm_head", params={"multiplier": self.logits_multiplier, "softcap": self.logit_softcap},
                         tensors={"head": self.lm_head if self.lm_head is not None else self.embedding},
                         parts={"norm": self.final_norm}, category="output")
 
@@ -125,6 +132,8 @@ class ModelSpec:
         refs = list(self.input_part().all_tensors())
         for layer in self.layers:
             refs.extend(layer.all_tensors())
+        for part in self.stream_parts.values():
+            refs.extend(part.all_tensors())
         refs.extend(self.output_part().all_tensors())
         for ref in refs:                       # (a tied head names the embedding table a second time)
             if ref.name not in seen:
@@ -138,6 +147,10 @@ class ModelSpec:
             if not 0 <= entry.layer < len(self.layers):
                 raise ConfigError(f"run order position {position} names layer {entry.layer}, "
                                   f"the model has {len(self.layers)}")
+            for name in entry.before:
+                if name not in self.stream_parts:
+                    raise ConfigError(f"run order position {position} names the stream part '{name}', the model "
+                                      f"has {', '.join(sorted(self.stream_parts)) or 'none'}")
             if entry.cache_of is not None:
                 if not 0 <= entry.cache_of < position:
                     raise ConfigError(f"run order position {position} reads the cache of position "

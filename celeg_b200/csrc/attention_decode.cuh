@@ -46,6 +46,7 @@ struct DecodeParams {
     float* partial_ml;             // [tokens, q_heads, max_splits, 2]
     int* counters;                 // [tokens, kv_heads], zero between launches
     int* error_flag;
+    const float* sinks;            // [q_heads] or null: a score per head that enters the denominator once (no key, no value)
     // Optional: the q/k post-processing of the step's own token done here instead of by a kernel of its
     // own. Then q (and the k and v behind it in the same rows: [q heads | k heads | v heads]) is the raw
     // projection; an item normalises and rotates its query heads itself, and the item whose keys include
@@ -415,7 +416,11 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
     if (tid < group) {
         float m = -INFINITY;
         for (int w = 0; w < kDecodeWarps; ++w) m = fmaxf(m, warp_max_s[w][tid]);
-        float sum = 0.0f;
+        // the sink joins the first split of a token's keys (in units of log2, like the maxima)
+        const bool with_sink = p.sinks != nullptr && split == 0;
+        const float sink_log2 = with_sink ? p.sinks[kvh * group + tid] * 1.4426950408889634f : -INFINITY;
+        m = fmaxf(m, sink_log2);
+        float sum = with_sink ? exp2f(sink_log2 - m) : 0.0f;
         for (int w = 0; w < kDecodeWarps; ++w)
             sum += warp_max_s[w][tid] == -INFINITY ? 0.0f : warp_sum_s[w][tid] * exp2f(warp_max_s[w][tid] - m);
         head_max[tid] = m;
@@ -773,7 +778,9 @@ __device__ __forceinline__ void attention_decode_item_solo(const DecodeParams& p
     for (int half = 0; half < 2; ++half) {
         const int r = g + half * 8;
         if (r >= group) continue;
-        const float inv = 1.0f / run_sum[half];
+        // (a sink adds its weight relative to the row's maximum to the denominator)
+        const float sink_part = p.sinks ? exp2f(p.sinks[kvh * group + r] * 1.4426950408889634f - run_max[half]) : 0.0f;
+        const float inv = 1.0f / (run_sum[half] + sink_part);
         __nv_bfloat16* dst = p.out + ((size_t)t * p.q_heads + kvh * group + r) * d;
 #pragma unroll
         for (int i = 0; i < kOTiles; ++i) {

@@ -4,6 +4,9 @@
 // (running maximum and denominator) in float32. A token's result depends only on its own keys,
 // read in position order, so it is the same bit for bit however the batch was cut.
 //
+// An optional sink per query head (a learned score that enters the denominator once, unscaled, with no
+// value) is where the running maximum and denominator start.
+//
 // This is the whole attention of the float32 path and the fall-back of the bfloat16 path for
 // head sizes the tensor-core kernels refuse.
 //
@@ -22,7 +25,8 @@ __global__ void attention_generic_kernel(const A* __restrict__ q, int q_row_stri
                                          const int* __restrict__ token_span,
                                          const int* __restrict__ block_table, int table_stride, int tokens,
                                          int q_heads, int kv_heads, int head_dim, int page_tokens, int window,
-                                         float scale, int* __restrict__ error_flag) {
+                                         float scale, const float* __restrict__ sinks,
+                                         int* __restrict__ error_flag) {
     extern __shared__ float q_smem[];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -42,8 +46,9 @@ __global__ void attention_generic_kernel(const A* __restrict__ q, int q_row_stri
     float acc[kAccRegs];
 #pragma unroll
     for (int r = 0; r < kAccRegs; ++r) acc[r] = 0.0f;
-    float running_max = -INFINITY;
-    float denom = 0.0f;
+    // a sink is a score without key or value: the softmax starts from it (weight 1 at the maximum so far)
+    float running_max = sinks ? sinks[h] : -INFINITY;
+    float denom = sinks ? 1.0f : 0.0f;
     const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
 
     for (int base = first_key; base <= pos; base += 32) {
@@ -103,7 +108,7 @@ CELEG_API int celeg_attention_generic(const void* q, int q_row_stride, void* out
                                       const void* v_cache, long long page_stride, const int* positions,
                                       const int* token_span, const int* block_table, int table_stride,
                                       int tokens, int q_heads, int kv_heads, int head_dim, int page_tokens,
-                                      int window, float scale, int* error_flag, int act_dtype,
+                                      int window, float scale, const float* sinks, int* error_flag, int act_dtype,
                                       cudaStream_t stream) {
     CELEG_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads > 0 && head_dim > 0 && page_tokens > 0,
                   "attention: invalid sizes tokens=%d q_heads=%d kv_heads=%d head_dim=%d page_tokens=%d", tokens,
@@ -120,12 +125,12 @@ CELEG_API int celeg_attention_generic(const void* q, int q_row_stride, void* out
         attention_generic_kernel<float><<<blocks, warps * 32, smem, stream>>>(
             (const float*)q, q_row_stride, (float*)out, (const float*)k_cache, (const float*)v_cache, page_stride,
             positions, token_span, block_table, table_stride, tokens, q_heads, kv_heads, head_dim, page_tokens,
-            window, scale, error_flag);
+            window, scale, sinks, error_flag);
     else if (act_dtype == kBFloat16)
         attention_generic_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
             (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
             (const __nv_bfloat16*)v_cache, page_stride, positions, token_span, block_table, table_stride, tokens,
-            q_heads, kv_heads, head_dim, page_tokens, window, scale, error_flag);
+            q_heads, kv_heads, head_dim, page_tokens, window, scale, sinks, error_flag);
     else
         CELEG_REQUIRE(false, "attention: unknown dtype code %d", act_dtype);
     return check_launch("attention_generic");

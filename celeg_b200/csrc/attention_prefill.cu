@@ -39,6 +39,7 @@ struct PrefillParams {
     int table_stride;
     int spans, q_heads, kv_heads, head_dim, page_tokens, window;
     float scale_log2;              // softmax scale * log2(e)
+    const float* sinks;            // [q_heads] or null: a score per head in the denominator, no key, no value
     int* error_flag;
 };
 
@@ -99,8 +100,12 @@ __global__ void __launch_bounds__(kPrefillThreads, D_PAD <= 64 ? 2 : 1) attentio
     for (int i = 0; i < kOTiles; ++i)
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[i][e] = 0.0f;
-    float run_max[2] = {-INFINITY, -INFINITY};
-    float run_sum[2] = {0.0f, 0.0f};
+    // with a sink the softmax of every row starts from it: maximum = the sink (in units of log2), sum = 1
+    // (in one of the four lanes that share a row: their sums are added up at the end)
+    const float sink_log2 = p.sinks ? p.sinks[blockIdx.x] * 1.4426950408889634f : -INFINITY;
+    const float sink_one = (p.sinks && (lane & 3) == 0) ? 1.0f : 0.0f;
+    float run_max[2] = {sink_log2, sink_log2};
+    float run_sum[2] = {sink_one, sink_one};
 
     const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
     const int q_row = warp * 16 + g;                 // this thread's first row; the second is q_row + 8
@@ -296,7 +301,7 @@ CELEG_API int celeg_attention_prefill(const void* q, int q_row_stride, void* out
                                       const void* v_cache, long long page_stride, const int* positions,
                                       const int* span_begin, const int* block_table, int table_stride,
                                       int tokens, int spans, int q_heads, int kv_heads, int head_dim,
-                                      int page_tokens, int window, float scale, int* error_flag,
+                                      int page_tokens, int window, float scale, const float* sinks, int* error_flag,
                                       cudaStream_t stream) {
     CELEG_REQUIRE(tokens >= 0 && spans >= 0 && q_heads > 0 && kv_heads > 0 && head_dim > 0 && page_tokens > 0,
                   "attention_prefill: invalid sizes tokens=%d spans=%d q_heads=%d kv_heads=%d head_dim=%d "
@@ -327,6 +332,7 @@ CELEG_API int celeg_attention_prefill(const void* q, int q_row_stride, void* out
     p.page_tokens = page_tokens;
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.sinks = sinks;
     p.error_flag = error_flag;
     const int tiles = (tokens + kBlockM - 1) / kBlockM + spans;      // upper bound on sum of ceil(len / 64)
     if (head_dim <= 64) return launch_prefill<64>(p, tiles, stream);

@@ -9,8 +9,30 @@ __global__ void qk_norm_rope_store_kernel(A* qkv, A* k_cache, A* v_cache, const 
     chain_wait();
     const int warps_per_block = blockDim.x >> 5;
     const long long unit = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-    if (unit >= (long long)args.tokens * (args.q_heads + 2 * args.kv_heads)) return;
+    if (unit >= (long long)args.tokens * (args.q_heads + (args.values_are_keys ? 1 : 2) * args.kv_heads)) return;
     qk_norm_rope_unit<A>(qkv, k_cache, v_cache, args, unit, threadIdx.x & 31);
+}
+
+// Norm over the whole projection: scales[t, 0 / 1] = 1 / sqrt(mean(x^2) + eps) over all q (all k) heads of token t.
+template <typename A>
+__global__ void qk_row_scales_kernel(const A* qkv, float* scales, int tokens, int row_width, int q_width, int k_width,
+                                     float eps) {
+    chain_release();
+    chain_wait();
+    const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= 2LL * tokens) return;
+    const int lane = threadIdx.x & 31;
+    const int t = (int)(unit >> 1), which = (int)(unit & 1);
+    const int width = which ? k_width : q_width;
+    if (width == 0) return;
+    const A* src = qkv + (size_t)t * row_width + (which ? q_width : 0);
+    float sum = 0.0f;
+    for (int i = lane; i < width; i += 32) {
+        const float x = to_float(load_l2(src + i));
+        sum += x * x;
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) scales[2 * (size_t)t + which] = 1.0f / sqrtf(sum / (float)width + eps);
 }
 
 // The common shape (rotation over the whole head, head size 64, 128 or 256, many tokens): a warp takes
@@ -238,7 +260,7 @@ CELEG_API int celeg_qk_norm_rope_store(void* qkv, const float* q_weight, const f
     if (!inv_freq) rotary_dim = head_dim & ~1;       // without rotation the pair loop just normalises
     const QkNormRopeArgs args = {q_weight, k_weight, inv_freq, positions, token_span, block_table, table_stride,
                                  page_stride, tokens, q_heads, kv_heads, head_dim, rotary_dim, page_tokens, eps,
-                                 store_kv, error_flag};
+                                 store_kv, error_flag, 0, nullptr, 0};
     // many tokens of the common shape: a warp per token and run of eight heads
     if (act_dtype == kBFloat16 && inv_freq && rotary_dim == head_dim && tokens >= 64 &&
         (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
@@ -280,4 +302,52 @@ CELEG_API int celeg_qk_norm_rope_store(void* qkv, const float* q_weight, const f
     else
         CELEG_REQUIRE(false, "qk_norm_rope_store: unknown dtype code %d", act_dtype);
     return check_launch("qk_norm_rope_store");
+}
+
+// The variant for attention whose q and k are normalised over the whole projection (weights
+// [q_heads * head_dim] and [kv_heads * head_dim], either may be null) and whose values are the keys as
+// projected: rows are [q heads | k heads]; q is normalised and rotated in place, k goes normalised and rotated
+// into k_cache and unchanged into v_cache. ``row_scales``: scratch of 2 * tokens floats. Two launches.
+CELEG_API int celeg_qk_whole_norm_rope_store(void* qk, const float* q_weight, const float* k_weight,
+                                             const float* inv_freq, const int* positions, const int* token_span,
+                                             const int* block_table, int table_stride, void* k_cache, void* v_cache,
+                                             long long page_stride, int tokens, int q_heads, int kv_heads,
+                                             int head_dim, int rotary_dim, int page_tokens, float eps,
+                                             int values_are_keys, float* row_scales, int* error_flag, int act_dtype,
+                                             cudaStream_t stream) {
+    CELEG_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads > 0 && head_dim > 0 && page_tokens > 0,
+                  "qk_whole_norm_rope_store: invalid sizes tokens=%d q_heads=%d kv_heads=%d head_dim=%d page_tokens=%d",
+                  tokens, q_heads, kv_heads, head_dim, page_tokens);
+    CELEG_REQUIRE(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
+                  "qk_whole_norm_rope_store: rotary_dim %d must be even and at most head_dim %d", rotary_dim, head_dim);
+    CELEG_REQUIRE(eps > 0.0f && row_scales, "qk_whole_norm_rope_store: eps must be positive and the scratch given");
+    CELEG_REQUIRE(act_dtype == kFloat32 || act_dtype == kBFloat16, "qk_whole_norm_rope_store: unknown dtype code %d",
+                  act_dtype);
+    if (tokens == 0) return 0;
+    const int heads = q_heads + (values_are_keys ? 1 : 2) * kv_heads;
+    const int warps = 4;
+    if (!inv_freq) rotary_dim = 0;
+    if (q_weight || k_weight) {
+        const unsigned blocks = (unsigned)((2LL * tokens + warps - 1) / warps);
+        if (act_dtype == kFloat32)
+            launch_chained(qk_row_scales_kernel<float>, blocks, warps * 32, 0, stream, (const float*)qk, row_scales,
+                           tokens, heads * head_dim, q_heads * head_dim, kv_heads * head_dim, eps);
+        else
+            launch_chained(qk_row_scales_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream, (const __nv_bfloat16*)qk,
+                           row_scales, tokens, heads * head_dim, q_heads * head_dim, kv_heads * head_dim, eps);
+        const int status = check_launch("qk_row_scales");
+        if (status != 0) return status;
+    }
+    const QkNormRopeArgs args = {q_weight, k_weight, inv_freq, positions, token_span, block_table, table_stride,
+                                 page_stride, tokens, q_heads, kv_heads, head_dim, rotary_dim, page_tokens, eps,
+                                 1, error_flag, 1, row_scales, values_are_keys ? 1 : 0};
+    const long long units = (long long)tokens * heads;
+    const unsigned blocks = (unsigned)((units + warps - 1) / warps);
+    if (act_dtype == kFloat32)
+        launch_chained(qk_norm_rope_store_kernel<float>, blocks, warps * 32, 0, stream, (float*)qk, (float*)k_cache,
+                       (float*)v_cache, args);
+    else
+        launch_chained(qk_norm_rope_store_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream, (__nv_bfloat16*)qk,
+                       (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, args);
+    return check_launch("qk_whole_norm_rope_store");
 }

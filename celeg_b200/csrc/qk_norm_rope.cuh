@@ -41,6 +41,11 @@ struct QkNormRopeArgs {
     int store_kv;      // 0: q heads only; 1: k (normalised, rotated) and v go to the cache; 2: k heads are
                        // normalised and rotated in place like q heads, v heads and the cache are left alone
     int* error_flag;
+    int whole_norm;    // 1: the RMS norm runs over all heads of q (of k) together, weights [q_heads * head_dim]
+                       // and [kv_heads * head_dim]; 0: per head, weights [head_dim]
+    const float* row_scales;   // whole_norm: [tokens, 2] = 1 / sqrt(mean square + eps) of each token's q and k
+    int values_are_keys;   // 1: rows are [q heads | k heads] only, and a key as projected (before norm and
+                           // rotation) is stored as its own value
 };
 
 // One warp: head `unit % heads` of token `unit / heads`, heads = q_heads + 2 kv_heads.
@@ -59,7 +64,7 @@ __device__ __forceinline__ void qk_norm_rope_unit(A* qkv, A* k_cache, A* v_cache
     const int page_tokens = a.page_tokens, store_kv = a.store_kv;
     const float eps = a.eps;
     int* error_flag = a.error_flag;
-    const int heads = q_heads + 2 * kv_heads;
+    const int heads = q_heads + (a.values_are_keys ? 1 : 2) * kv_heads;
     const int t = (int)(unit / heads);
     const int h = (int)(unit % heads);
     A* vec = qkv + ((size_t)t * heads + h) * head_dim;
@@ -81,13 +86,50 @@ __device__ __forceinline__ void qk_norm_rope_unit(A* qkv, A* k_cache, A* v_cache
             return;
         }
         A* base = is_k ? k_cache : v_cache;
-        dst = base + (size_t)page * page_stride + ((size_t)kvh * page_tokens + (pos % page_tokens)) * head_dim;
+        const size_t cache_at = (size_t)page * page_stride + ((size_t)kvh * page_tokens + (pos % page_tokens)) * head_dim;
+        dst = base + cache_at;
+        if (is_k && a.values_are_keys) {             // the key as projected is the value
+            for (int i = lane; i < head_dim; i += 32) v_cache[cache_at + i] = load_l2(vec + i);
+        }
     }
     if (!is_q && !is_k) {                            // v: plain copy
         for (int i = lane; i < head_dim; i += 32) dst[i] = load_l2(vec + i);
         return;
     }
     const float* weight = is_q ? q_weight : k_weight;
+    if (a.whole_norm) {
+        // one scale for all heads of the token's q (or k), computed by a launch before this one (heads are
+        // rewritten in place, so no warp of this launch may read another head)
+        float inv_all = 1.0f;
+        if (weight) {
+            inv_all = a.row_scales[2 * (size_t)t + (is_q ? 0 : 1)];
+            weight += (size_t)(is_q ? h : kvh) * head_dim;
+        }
+        const int half = rotary_dim >> 1;
+        for (int i = lane; i < half; i += 32) {
+            float x = to_float(load_l2(vec + i));
+            float y = to_float(load_l2(vec + i + half));
+            if (weight) {
+                x = x * inv_all * weight[i];
+                y = y * inv_all * weight[i + half];
+            }
+            float rx = x, ry = y;
+            if (inv_freq) {
+                float sn, cs;
+                sincosf((float)pos * inv_freq[i], &sn, &cs);
+                rx = x * cs - y * sn;
+                ry = y * cs + x * sn;
+            }
+            dst[i] = from_float<A>(rx);
+            dst[i + half] = from_float<A>(ry);
+        }
+        for (int i = rotary_dim + lane; i < head_dim; i += 32) {
+            float x = to_float(load_l2(vec + i));
+            if (weight) x = x * inv_all * weight[i];
+            dst[i] = from_float<A>(x);
+        }
+        return;
+    }
     if (inv_freq && rotary_dim == head_dim && (head_dim & 63) == 0 && head_dim <= 256) {
         // the common shape in one pass: a lane holds its pairs (i, i + half) in registers between the
         // sum of squares and the rotation, so the row is read once and every load is in flight at once

@@ -1,0 +1,407 @@
+// Mixers whose cache is a matrix per head that every token rewrites: the mLSTM matrix memory and the gated
+// delta rule. State, gates and every sum are float32 on both precision paths.
+//
+// The recurrences, per head, with S [dim, vdim] (and for the mLSTM a normaliser n [dim] and a running
+// maximum m that starts at 0):
+//
+//   mLSTM   m' = max(f + m, i);  a = exp(f + m - m'),  b = exp(i - m')
+//           S' = a S + b k v^T;  n' = a n + b k;  o = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6)
+//   delta   S~ = g S;  u = beta (v - S~^T k);  S' = S~ + k u^T;  o = S'^T q
+//
+// Column j of S depends on column j alone, so a launch is cut by (span, head, run of columns) and walks the
+// span's tokens in order. A column lives in the registers of L lanes (L = 1, 2, 4 or 8 by the key size, 32
+// elements a lane); per token the lanes form S.k, S.q (and n.q) on the OLD state together, exchange them with
+// shuffles once, and get the read-out from them without a second pass over the new state:
+//   delta: o_j = g (S.q)_j + u_j (k.q)         mLSTM: (S'^T q)_j = a (S.q)_j + b v_j (k.q),  n'.q = a n.q + b k.q
+// Keys, queries, values and gates of the next 16 tokens are copied to shared memory (cp.async) while the
+// current 16 are worked on. A span of one token (decoding) is the same kernel: one state read, one write.
+//
+// Beside the scans: the gates of both mixers from their projections, the delta rule's short convolutions with
+// their carried inputs, unit norms and decay, and the per-head norm with the output gate.
+#include "common.cuh"
+
+namespace celeg_b200 {
+
+constexpr int kScanRegs = 32;        // elements of a column a lane holds
+constexpr int kScanTile = 16;        // tokens staged at a time (8 when a column takes 8 lanes: shared memory)
+constexpr int kScanMaxDim = 256;
+
+enum ScanMode : int { kScanDelta = 0, kScanMlstm = 1 };
+
+struct ScanParams {
+    const float* q; const float* k; const float* v;     // rows of the step's tokens; head h at h * dim (h * vdim)
+    int q_stride, k_stride, v_stride;
+    const float* gates;                                  // [tokens, 2 * heads]: delta (beta, g); mLSTM (i, f), logs
+    float* out;                                          // [tokens, heads * vdim]
+    float* state;                                        // this part's floats inside slot 0
+    long long slot_stride;
+    const int* span_begin; const int* span_slot;
+    int heads, kv_heads, dim, vdim;
+    float q_scale;
+};
+
+__device__ __forceinline__ void cp_async_4(void* smem, const void* global) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(global));
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+// One warp a block. Element e of a column sits in lane (e / 4) % L, register 4 * (e / (4 L)) + e % 4, so that
+// the lanes of a column read consecutive 16-byte pieces of a key.
+template <int MODE, int L>
+__global__ void __launch_bounds__(32) recurrent_scan_kernel(const ScanParams p) {
+    constexpr int kCols = 32 / L;
+    constexpr int kDimPad = kScanRegs * L;
+    constexpr int kTile = L == 8 ? kScanTile / 2 : kScanTile;
+    __shared__ __align__(16) float k_s[2][kTile][kDimPad];
+    __shared__ __align__(16) float q_s[2][kTile][kDimPad];
+    __shared__ float v_s[2][kTile][kCols];
+    __shared__ float g_s[2][kTile][2];
+    chain_release();
+    const int lane = threadIdx.x;
+    const int sub = lane % L, col_in = lane / L;
+    const int head = blockIdx.y, span = blockIdx.z;
+    const int kv_head = head / (p.heads / p.kv_heads);
+    const int col = blockIdx.x * kCols + col_in;
+    const bool col_ok = col < p.vdim;
+    const int dim = p.dim, vdim = p.vdim;
+    // keys beyond the head's size stay zero for good
+    for (int i = lane; i < 2 * kTile * kDimPad; i += 32) {
+        (&k_s[0][0][0])[i] = 0.0f;
+        (&q_s[0][0][0])[i] = 0.0f;
+    }
+    chain_wait();
+    const int t_begin = p.span_begin[span], t_end = p.span_begin[span + 1];
+    if (t_end <= t_begin) return;
+    float* slot = p.state + (long long)p.span_slot[span] * p.slot_stride;
+    float* s_head = slot + (size_t)head * dim * vdim;
+    float* n_head = slot + (size_t)p.heads * dim * vdim + (size_t)head * dim;
+    float* m_head = slot + (size_t)p.heads * dim * vdim + (size_t)p.heads * dim + head;
+
+    float s[kScanRegs], n[MODE == kScanMlstm ? kScanRegs : 1];
+#pragma unroll
+    for (int r = 0; r < kScanRegs; ++r) {
+        const int e = 4 * ((r >> 2) * L + sub) + (r & 3);
+        s[r] = (col_ok && e < dim) ? s_head[(size_t)e * vdim + col] : 0.0f;
+        if (MODE == kScanMlstm) n[r] = e < dim ? n_head[e] : 0.0f;
+    }
+    float m = MODE == kScanMlstm ? *m_head : 0.0f;
+    __syncwarp();
+
+    auto issue = [&](int t0, int stage) {
+        const int count = min(kTile, t_end - t0);
+        for (int i = lane; i < count * dim; i += 32) {
+            const int tt = i / dim, e = i % dim;
+            cp_async_4(&k_s[stage][tt][e], p.k + (size_t)(t0 + tt) * p.k_stride + (size_t)kv_head * dim + e);
+            cp_async_4(&q_s[stage][tt][e], p.q + (size_t)(t0 + tt) * p.q_stride +
+                                               (size_t)(MODE == kScanMlstm ? head : kv_head) * dim + e);
+        }
+        for (int i = lane; i < count * kCols; i += 32) {
+            const int tt = i / kCols, c = i % kCols;
+            const int gc = blockIdx.x * kCols + c;
+            if (gc < vdim) cp_async_4(&v_s[stage][tt][c], p.v + (size_t)(t0 + tt) * p.v_stride + (size_t)head * vdim + gc);
+        }
+        for (int i = lane; i < count * 2; i += 32) {
+            const int tt = i / 2, w = i % 2;
+            cp_async_4(&g_s[stage][tt][w], p.gates + (size_t)(t0 + tt) * 2 * p.heads + w * p.heads + head);
+        }
+        cp_async_commit_group();
+    };
+
+    issue(t_begin, 0);
+    int stage = 0;
+    for (int t0 = t_begin; t0 < t_end; t0 += kTile, stage ^= 1) {
+        if (t0 + kTile < t_end) {
+            issue(t0 + kTile, stage ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncwarp();
+        const int count = min(kTile, t_end - t0);
+        for (int tt = 0; tt < count; ++tt) {
+            float kk[kScanRegs], qq[kScanRegs];
+#pragma unroll
+            for (int r4 = 0; r4 < kScanRegs / 4; ++r4) {
+                const float4 kv4 = *reinterpret_cast<const float4*>(&k_s[stage][tt][4 * (r4 * L + sub)]);
+                const float4 qv4 = *reinterpret_cast<const float4*>(&q_s[stage][tt][4 * (r4 * L + sub)]);
+                kk[4 * r4] = kv4.x; kk[4 * r4 + 1] = kv4.y; kk[4 * r4 + 2] = kv4.z; kk[4 * r4 + 3] = kv4.w;
+                qq[4 * r4] = qv4.x; qq[4 * r4 + 1] = qv4.y; qq[4 * r4 + 2] = qv4.z; qq[4 * r4 + 3] = qv4.w;
+            }
+            // four partial sums each, so that no chain of dependent additions is longer than a quarter
+            float sk[4] = {0.f, 0.f, 0.f, 0.f}, sq[4] = {0.f, 0.f, 0.f, 0.f}, kq[4] = {0.f, 0.f, 0.f, 0.f};
+            float nq[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int r = 0; r < kScanRegs; ++r) {
+                if (MODE == kScanDelta) sk[r & 3] = fmaf(s[r], kk[r], sk[r & 3]);
+                sq[r & 3] = fmaf(s[r], qq[r], sq[r & 3]);
+                kq[r & 3] = fmaf(kk[r], qq[r], kq[r & 3]);
+                if (MODE == kScanMlstm) nq[r & 3] = fmaf(n[r], qq[r], nq[r & 3]);
+            }
+            float d_sk = (sk[0] + sk[1]) + (sk[2] + sk[3]);
+            float d_sq = (sq[0] + sq[1]) + (sq[2] + sq[3]);
+            float d_kq = (kq[0] + kq[1]) + (kq[2] + kq[3]);
+            float d_nq = (nq[0] + nq[1]) + (nq[2] + nq[3]);
+#pragma unroll
+            for (int offset = 1; offset < L; offset <<= 1) {
+                if (MODE == kScanDelta) d_sk += __shfl_xor_sync(0xffffffffu, d_sk, offset);
+                d_sq += __shfl_xor_sync(0xffffffffu, d_sq, offset);
+                d_kq += __shfl_xor_sync(0xffffffffu, d_kq, offset);
+                if (MODE == kScanMlstm) d_nq += __shfl_xor_sync(0xffffffffu, d_nq, offset);
+            }
+            d_sq *= p.q_scale;
+            d_kq *= p.q_scale;
+            d_nq *= p.q_scale;
+            const float vj = v_s[stage][tt][col_in];
+            const float g0 = g_s[stage][tt][0], g1 = g_s[stage][tt][1];
+            float o;
+            if (MODE == kScanDelta) {
+                const float beta = g0, decay = g1;
+                const float u = beta * (vj - decay * d_sk);
+                o = decay * d_sq + u * d_kq;
+#pragma unroll
+                for (int r = 0; r < kScanRegs; ++r) s[r] = fmaf(kk[r], u, decay * s[r]);
+            } else {
+                const float m_new = fmaxf(g1 + m, g0);
+                const float keep = expf(g1 + m - m_new), write = expf(g0 - m_new);
+                m = m_new;
+                const float bv = write * vj;
+                const float upper = keep * d_sq + bv * d_kq;
+                const float lower = fmaxf(fabsf(keep * d_nq + write * d_kq), expf(-m_new)) + 1e-6f;
+                o = upper / lower;
+#pragma unroll
+                for (int r = 0; r < kScanRegs; ++r) {
+                    s[r] = fmaf(kk[r], bv, keep * s[r]);
+                    n[r] = fmaf(kk[r], write, keep * n[r]);
+                }
+            }
+            if (sub == 0 && col_ok) p.out[(size_t)(t0 + tt) * p.heads * vdim + (size_t)head * vdim + col] = o;
+        }
+        __syncwarp();                                   // the stage is free for the tile after the next
+    }
+#pragma unroll
+    for (int r = 0; r < kScanRegs; ++r) {
+        const int e = 4 * ((r >> 2) * L + sub) + (r & 3);
+        if (col_ok && e < dim) s_head[(size_t)e * vdim + col] = s[r];
+        if (MODE == kScanMlstm && blockIdx.x == 0 && col_in == 0 && e < dim) n_head[e] = n[r];
+    }
+    if (MODE == kScanMlstm && blockIdx.x == 0 && lane == 0) *m_head = m;
+}
+
+// mLSTM: log input gate cap tanh((x_i + b_i) / cap) and log forget gate logsigmoid(cap tanh((x_f + b_f) / cap))
+__global__ void mlstm_gates_kernel(const float* pre_i, const float* pre_f, int stride, const float* bias_i,
+                                   const float* bias_f, float cap, float* gates, int tokens, int heads) {
+    chain_release();
+    chain_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= tokens * heads) return;
+    const int t = i / heads, h = i % heads;
+    const float gi = cap * tanhf((pre_i[(size_t)t * stride + h] + bias_i[h]) / cap);
+    const float z = cap * tanhf((pre_f[(size_t)t * stride + h] + bias_f[h]) / cap);
+    // logsigmoid(z) = min(z, 0) - log1p(exp(-|z|))
+    const float gf = fminf(z, 0.0f) - log1pf(expf(-fabsf(z)));
+    gates[(size_t)t * 2 * heads + h] = gi;
+    gates[(size_t)t * 2 * heads + heads + h] = gf;
+}
+
+struct DeltaPrepareArgs {
+    const float* proj; int stride;          // rows [q | k | v | ...]: the first `channels` columns are convolved
+    const float* kernel;                    // [channels, taps], the last tap multiplies the token itself
+    const float* carried;                   // this part's carried inputs inside slot 0: [taps - 1, channels], oldest first
+    long long slot_stride;
+    const int* token_span; const int* span_begin; const int* span_slot;
+    float* conv_out;                        // [tokens, channels]: silu(conv); q and k heads made unit vectors
+    const float* pre_beta; const float* pre_a; int gate_stride;
+    const float* a_log; const float* dt_bias;
+    float* gates;                           // [tokens, 2 * heads]: beta, decay
+    int tokens, channels, taps, qk_heads, dim, heads;
+    float unit_eps;
+};
+
+// One block a token: the three short convolutions with SiLU, then q and k per head divided by
+// sqrt(sum of squares + eps), then beta = sigmoid(.) and decay = exp(-exp(A_log) softplus(. + dt_bias)).
+__global__ void delta_prepare_kernel(const DeltaPrepareArgs a) {
+    extern __shared__ float row[];          // [channels]
+    chain_release();
+    chain_wait();
+    const int t = blockIdx.x;
+    const int span = a.token_span[t];
+    const int begin = a.span_begin[span];
+    const float* carried = a.carried + (long long)a.span_slot[span] * a.slot_stride;
+    const int rel = t - begin;
+    for (int c = threadIdx.x; c < a.channels; c += blockDim.x) {
+        float sum = 0.0f;
+        for (int j = 0; j < a.taps; ++j) {
+            const int s = rel - (a.taps - 1) + j;
+            const float x = s >= 0 ? a.proj[(size_t)(begin + s) * a.stride + c]
+                                   : carried[(size_t)(a.taps - 1 + s) * a.channels + c];
+            sum = fmaf(a.kernel[(size_t)c * a.taps + j], x, sum);
+        }
+        row[c] = sum / (1.0f + expf(-sum));
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int h = warp; h < 2 * a.qk_heads; h += warps) {     // q heads, then k heads
+        float sum = 0.0f;
+        for (int i = lane; i < a.dim; i += 32) sum += row[h * a.dim + i] * row[h * a.dim + i];
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sqrtf(sum + a.unit_eps);
+        for (int i = lane; i < a.dim; i += 32) row[h * a.dim + i] *= inv;
+    }
+    __syncthreads();
+    float* dst = a.conv_out + (size_t)t * a.channels;
+    for (int c = threadIdx.x; c < a.channels; c += blockDim.x) dst[c] = row[c];
+    for (int h = threadIdx.x; h < a.heads; h += blockDim.x) {
+        const float b = a.pre_beta[(size_t)t * a.gate_stride + h];
+        const float x = a.pre_a[(size_t)t * a.gate_stride + h] + a.dt_bias[h];
+        const float soft = fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x)));
+        a.gates[(size_t)t * 2 * a.heads + h] = 1.0f / (1.0f + expf(-b));
+        a.gates[(size_t)t * 2 * a.heads + a.heads + h] = expf(-expf(a.a_log[h]) * soft);
+    }
+}
+
+// The carried inputs after a step: the last taps - 1 inputs of each request's sequence. One thread per
+// (span, channel) reads everything it needs before it writes, so the update is in place.
+__global__ void carried_inputs_update_kernel(const float* proj, int stride, float* carried, long long slot_stride,
+                                             const int* span_begin, const int* span_slot, int spans, int channels,
+                                             int taps) {
+    chain_release();
+    chain_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= spans * channels) return;
+    const int span = i / channels, c = i % channels;
+    const int begin = span_begin[span], len = span_begin[span + 1] - begin;
+    float* mine = carried + (long long)span_slot[span] * slot_stride;
+    float keep[15];
+#pragma unroll
+    for (int r = 0; r < 15; ++r) {
+        if (r < taps - 1) {
+            const int s = len - (taps - 1) + r;
+            keep[r] = s >= 0 ? proj[(size_t)(begin + s) * stride + c] : mine[(size_t)(taps - 1 + s) * channels + c];
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 15; ++r)
+        if (r < taps - 1) mine[(size_t)r * channels + c] = keep[r];
+}
+
+// One warp per (token, head): o / sqrt(mean(o^2) + eps) * w * act(gate), act = sigmoid (0) or SiLU (1);
+// w is [heads * vdim] or, shared by the heads, [vdim].
+template <typename A>
+__global__ void gated_head_norm_kernel(const float* o, const float* gate, int gate_stride, const float* weight,
+                                       int weight_per_head, A* out, int tokens, int heads, int vdim, float eps,
+                                       int gate_kind) {
+    chain_release();
+    chain_wait();
+    const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= (long long)tokens * heads) return;
+    const int lane = threadIdx.x & 31;
+    const int t = (int)(unit / heads), h = (int)(unit % heads);
+    const float* src = o + ((size_t)t * heads + h) * vdim;
+    float sum = 0.0f;
+    for (int i = lane; i < vdim; i += 32) sum += src[i] * src[i];
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sqrtf(sum / (float)vdim + eps);
+    const float* w = weight + (weight_per_head ? (size_t)h * vdim : 0);
+    const float* g = gate + (size_t)t * gate_stride + (size_t)h * vdim;
+    A* dst = out + ((size_t)t * heads + h) * vdim;
+    for (int i = lane; i < vdim; i += 32) {
+        const float z = g[i];
+        const float sig = 1.0f / (1.0f + expf(-z));
+        dst[i] = from_float<A>(src[i] * inv * w[i] * (gate_kind == 0 ? sig : z * sig));
+    }
+}
+
+template <int MODE>
+static int launch_scan(const ScanParams& p, int spans, cudaStream_t stream) {
+    const int lanes = p.dim <= 32 ? 1 : p.dim <= 64 ? 2 : p.dim <= 128 ? 4 : 8;
+    const int cols = 32 / lanes;
+    dim3 grid((p.vdim + cols - 1) / cols, p.heads, spans);
+    if (lanes == 1) launch_chained(recurrent_scan_kernel<MODE, 1>, grid, 32, 0, stream, p);
+    else if (lanes == 2) launch_chained(recurrent_scan_kernel<MODE, 2>, grid, 32, 0, stream, p);
+    else if (lanes == 4) launch_chained(recurrent_scan_kernel<MODE, 4>, grid, 32, 0, stream, p);
+    else launch_chained(recurrent_scan_kernel<MODE, 8>, grid, 32, 0, stream, p);
+    return check_launch("recurrent_scan");
+}
+
+}  // namespace celeg_b200
+
+using namespace celeg_b200;
+
+// mode 0: gated delta rule (q heads = kv_heads, gates = beta | decay); mode 1: mLSTM (q heads = heads,
+// gates = log input | log forget; the slot holds S, then n [heads, dim], then m [heads]).
+CELEG_API int celeg_recurrent_scan(int mode, const float* q, int q_stride, const float* k, int k_stride, const float* v,
+                                   int v_stride, const float* gates, float* out, float* state, long long slot_stride,
+                                   const int* span_begin, const int* span_slot, int spans, int heads, int kv_heads,
+                                   int dim, int vdim, float q_scale, cudaStream_t stream) {
+    CELEG_REQUIRE(spans >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0,
+                  "recurrent_scan: invalid sizes spans=%d heads=%d kv_heads=%d dim=%d vdim=%d", spans, heads, kv_heads,
+                  dim, vdim);
+    CELEG_REQUIRE(dim <= kScanMaxDim, "recurrent_scan: a key size of %d exceeds %d", dim, kScanMaxDim);
+    CELEG_REQUIRE(mode == kScanDelta || mode == kScanMlstm, "recurrent_scan: unknown mode %d", mode);
+    CELEG_REQUIRE(spans <= 65535 && heads <= 65535, "recurrent_scan: %d spans or %d heads exceed one launch", spans, heads);
+    if (spans == 0) return 0;
+    const ScanParams p = {q, k, v, q_stride, k_stride, v_stride, gates, out, state, slot_stride, span_begin, span_slot,
+                          heads, kv_heads, dim, vdim, q_scale};
+    return mode == kScanDelta ? launch_scan<kScanDelta>(p, spans, stream) : launch_scan<kScanMlstm>(p, spans, stream);
+}
+
+CELEG_API int celeg_mlstm_gates(const float* pre_i, const float* pre_f, int stride, const float* bias_i,
+                                const float* bias_f, float cap, float* gates, int tokens, int heads,
+                                cudaStream_t stream) {
+    CELEG_REQUIRE(tokens >= 0 && heads > 0 && cap > 0.0f, "mlstm_gates: invalid sizes tokens=%d heads=%d cap=%g", tokens,
+                  heads, cap);
+    if (tokens == 0) return 0;
+    const long long units = (long long)tokens * heads;
+    launch_chained(mlstm_gates_kernel, (unsigned)((units + 127) / 128), 128, 0, stream, pre_i, pre_f, stride, bias_i,
+                   bias_f, cap, gates, tokens, heads);
+    return check_launch("mlstm_gates");
+}
+
+CELEG_API int celeg_delta_prepare(const float* proj, int stride, const float* kernel, float* carried,
+                                  long long slot_stride, const int* token_span, const int* span_begin,
+                                  const int* span_slot, float* conv_out, const float* pre_beta, const float* pre_a,
+                                  const float* a_log, const float* dt_bias, float* gates, int tokens, int spans,
+                                  int channels, int taps, int qk_heads, int dim, int heads, float unit_eps,
+                                  cudaStream_t stream) {
+    CELEG_REQUIRE(tokens >= 0 && spans >= 0 && channels > 0 && taps >= 1 && taps <= 16 && qk_heads > 0 && dim > 0 &&
+                  heads > 0 && 2 * qk_heads * dim <= channels,
+                  "delta_prepare: invalid sizes tokens=%d channels=%d taps=%d qk_heads=%d dim=%d heads=%d", tokens,
+                  channels, taps, qk_heads, dim, heads);
+    CELEG_REQUIRE((size_t)channels * sizeof(float) <= 48 * 1024, "delta_prepare: %d channels exceed a block's shared memory",
+                  channels);
+    if (tokens == 0) return 0;
+    const DeltaPrepareArgs args = {proj, stride, kernel, carried, slot_stride, token_span, span_begin, span_slot,
+                                   conv_out, pre_beta, pre_a, stride, a_log, dt_bias, gates, tokens, channels, taps,
+                                   qk_heads, dim, heads, unit_eps};
+    launch_chained(delta_prepare_kernel, tokens, 256, (size_t)channels * sizeof(float), stream, args);
+    int status = check_launch("delta_prepare");
+    if (status != 0 || taps == 1) return status;
+    const long long units = (long long)spans * channels;
+    launch_chained(carried_inputs_update_kernel, (unsigned)((units + 127) / 128), 128, 0, stream, proj, stride, carried,
+                   slot_stride, span_begin, span_slot, spans, channels, taps);
+    return check_launch("carried_inputs_update");
+}
+
+CELEG_API int celeg_gated_head_norm(const float* o, const float* gate, int gate_stride, const float* weight,
+                                    int weight_per_head, void* out, int tokens, int heads, int vdim, float eps,
+                                    int gate_kind, int act_dtype, cudaStream_t stream) {
+    CELEG_REQUIRE(tokens >= 0 && heads > 0 && vdim > 0 && eps > 0.0f && (gate_kind == 0 || gate_kind == 1),
+                  "gated_head_norm: invalid sizes tokens=%d heads=%d vdim=%d eps=%g gate=%d", tokens, heads, vdim, eps,
+                  gate_kind);
+    if (tokens == 0) return 0;
+    const long long units = (long long)tokens * heads;
+    const unsigned blocks = (unsigned)((units + 3) / 4);
+    if (act_dtype == kFloat32)
+        launch_chained(gated_head_norm_kernel<float>, blocks, 128, 0, stream, o, gate, gate_stride, weight,
+                       weight_per_head, (float*)out, tokens, heads, vdim, eps, gate_kind);
+    else if (act_dtype == kBFloat16)
+        launch_chained(gated_head_norm_kernel<__nv_bfloat16>, blocks, 128, 0, stream, o, gate, gate_stride, weight,
+                       weight_per_head, (__nv_bfloat16*)out, tokens, heads, vdim, eps, gate_kind);
+    else
+        CELEG_REQUIRE(false, "gated_head_norm: unknown dtype code %d", act_dtype);
+    return check_launch("gated_head_norm");
+}

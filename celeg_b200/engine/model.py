@@ -71,6 +71,8 @@ class Model:
         # names others)
         self.input = build_part("input", spec.input_part(), tensors, rt)
         self.output = build_part("output", spec.output_part(), tensors, rt)
+        # parts that rewrite the stream between two blocks, run before the positions that name them
+        self.stream_parts = {name: build_part("stream", part, tensors, rt) for name, part in spec.stream_parts.items()}
         rt.release_sources()
         self.stream = ResidualStream(rt, spec.hidden_size)
         self.residual = self.stream.residual
@@ -155,7 +157,7 @@ class Model:
     def weight_tensors(self) -> List[torch.Tensor]:
         """Every tensor that a part of the model holds (the ends' and the layers'), each once."""
         found, seen = [], set()
-        holders = [self.input, self.output, getattr(self.output, "norm", None)]
+        holders = [self.input, self.output, getattr(self.output, "norm", None), *self.stream_parts.values()]
         for layer in self.layers:
             holders.extend(layer.parts.values())
         for holder in holders:
@@ -186,7 +188,11 @@ class Model:
             layer = self.layers[entry.layer]
             if self._rebind:
                 self._bind(position)
+            for name in entry.before:
+                self.stream_parts[name].run(stream, step)
             stream.after_layer = firsts[position + 1] if position + 1 < len(blocks) else head_norm
+            if position + 1 < len(blocks) and self.order[position + 1].before:
+                stream.after_layer = None           # (a stream part reads the stream next, not that block's norm)
             layer.block.run(stream, step)
         stream.after_layer = None
         if n_logits == 0:

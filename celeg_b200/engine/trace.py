@@ -36,8 +36,10 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines: IO[
     if PAGE_ROUNDING % page_tokens and page_tokens % PAGE_ROUNDING:
         raise ValueError(f"page size {page_tokens} neither divides nor is a multiple of {PAGE_ROUNDING}")
     batch_limit = max_batched_tokens or min(max(max_tokens, PAGE_ROUNDING), MAX_STEP_TOKENS)
+    # (no request can hold more positions than the pool has: block tables need not be longer than that)
     loaded = load_model(model_dir, dtype=dtype, device=device, cache_tokens=max_tokens, page_tokens=page_tokens,
-                        max_requests=max_requests, max_batched_tokens=batch_limit)
+                        max_requests=max_requests, max_batched_tokens=batch_limit,
+                        max_context=max(max_tokens, PAGE_ROUNDING))
     step_fn = loaded.step
     with open(os.path.join(out_dir, "model.json"), "w", encoding="utf-8") as handle:
         json.dump({"model_fingerprint": loaded.fingerprint, "dtype": str(dtype),
@@ -104,10 +106,11 @@ def main(argv=None) -> int:
                         help="most tokens live requests hold at any time, each rounded up to 64")
     parser.add_argument("--device", default="cuda:0")
     parser.add_argument("--page-tokens", type=int, default=None)
+    parser.add_argument("--max-requests", type=int, default=4, help="state slots: most requests live at a time")
     args = parser.parse_args(argv)
     try:
         return replay(args.model, args.dtype, args.out, args.max_tokens, sys.stdin, sys.stdout,
-                      device=args.device, page_tokens=args.page_tokens)
+                      device=args.device, page_tokens=args.page_tokens, max_requests=args.max_requests)
     except Exception as exc:  # one line for the user, non-zero exit
         print(f"error: {type(exc).__name__}: {exc}", file=sys.stderr, flush=True)
         return 1

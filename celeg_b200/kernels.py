@@ -45,8 +45,8 @@ _SIGNATURES = {
                                  c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                  c_int, c_void_p, c_int, c_void_p],
     "celeg_attention_generic": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
-                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int,
-                                c_void_p],
+                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+                                c_int, c_void_p],
     "celeg_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -58,7 +58,7 @@ _SIGNATURES = {
     "celeg_attention_decode_resident_blocks": [c_int],
     "celeg_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                c_void_p, c_void_p],
+                                c_void_p, c_void_p, c_void_p],
     "celeg_attention_prefill_tcgen05": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                         c_float, c_void_p, c_void_p],
@@ -80,6 +80,26 @@ _SIGNATURES = {
     "celeg_sample_greedy": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_void_p],
     "celeg_mark_seen": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "celeg_attention_decode_sinks": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "celeg_qk_whole_norm_rope_store": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                       c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                       c_int, c_void_p, c_void_p, c_int, c_void_p],
+    "celeg_add_dyt": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
+                      c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p],
+    "celeg_join_stream_embedding": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                    c_float, c_int, c_void_p],
+    "celeg_activation": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p],
+    "celeg_softcap": [c_void_p, c_longlong, c_float, c_void_p],
+    "celeg_recurrent_scan": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                             c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "celeg_mlstm_gates": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p],
+    "celeg_delta_prepare": [c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_int, c_float, c_void_p],
+    "celeg_gated_head_norm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_int,
+                              c_int, c_void_p],
 }
 
 
@@ -216,14 +236,38 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_we
         _stream()))
 
 
+def qk_whole_norm_rope_store(qk: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                             inv_freq: Optional[torch.Tensor], positions: torch.Tensor, token_span: torch.Tensor,
+                             block_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tokens: int,
+                             q_heads: int, kv_heads: int, head_dim: int, rotary_dim: int, page_tokens: int, eps: float,
+                             values_are_keys: bool, row_scales: torch.Tensor, error_flag: torch.Tensor) -> None:
+    """q and k normalised over the whole projection (weights [q_heads*head_dim], [kv_heads*head_dim]), rotated, q in
+    place, k into the cache; ``values_are_keys``: rows are [q heads | k heads] and a key as projected is stored as
+    its own value (else rows are [q | k | v heads]). ``row_scales``: float32 scratch of 2*tokens."""
+    _need(row_scales, torch.float32, "row_scales")
+    assert row_scales.numel() >= 2 * tokens
+    _check(library().celeg_qk_whole_norm_rope_store(
+        _ptr(qk), _ptr(q_weight), _ptr(k_weight), _ptr(inv_freq), _ptr(positions), _ptr(token_span),
+        _ptr(block_table), block_table.stride(0), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), tokens, q_heads,
+        kv_heads, head_dim, rotary_dim, page_tokens, eps, int(values_are_keys), _ptr(row_scales), _ptr(error_flag),
+        dtype_code(qk.dtype), _stream()))
+    global LAUNCHES
+    LAUNCHES += 1 if (q_weight is not None or k_weight is not None) else 0      # the scales are a launch of their own
+
+
 def attention_generic(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_cache: torch.Tensor,
                       v_cache: torch.Tensor, positions: torch.Tensor, token_span: torch.Tensor,
                       block_table: torch.Tensor, tokens: int, q_heads: int, kv_heads: int, head_dim: int,
-                      page_tokens: int, window: Optional[int], scale: float, error_flag: torch.Tensor) -> None:
+                      page_tokens: int, window: Optional[int], scale: float, error_flag: torch.Tensor,
+                      sinks: Optional[torch.Tensor] = None) -> None:
+    """``sinks``: float32 [q_heads] or None; a head's sink is a score that enters the denominator of each of its
+    rows once, unscaled, without key or value."""
+    if sinks is not None:
+        _need(sinks, torch.float32, "sinks")
     _check(library().celeg_attention_generic(
         _ptr(q), q_row_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), _ptr(positions),
         _ptr(token_span), _ptr(block_table), block_table.stride(0), tokens, q_heads, kv_heads, head_dim,
-        page_tokens, int(window or 0), scale, _ptr(error_flag), dtype_code(q.dtype), _stream()))
+        page_tokens, int(window or 0), scale, _ptr(sinks), _ptr(error_flag), dtype_code(q.dtype), _stream()))
 
 
 def attention_decode_supported(q_heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
@@ -242,13 +286,22 @@ def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_ca
                      block_table: torch.Tensor, tokens: int, q_heads: int, kv_heads: int, head_dim: int,
                      page_tokens: int, window: Optional[int], scale: float, chunk: int, max_splits: int,
                      partial_o: torch.Tensor, partial_ml: torch.Tensor, counters: torch.Tensor,
-                     error_flag: torch.Tensor) -> None:
+                     error_flag: torch.Tensor, sinks: Optional[torch.Tensor] = None) -> None:
     """One query token per row, keys split into chunks of ``chunk``; scratch: partial_o float32
     [tokens*q_heads*max_splits*head_dim], partial_ml float32 [tokens*q_heads*max_splits*2],
-    counters int32 [tokens*kv_heads] (zero before the first call, left zero by every call)."""
+    counters int32 [tokens*kv_heads] (zero before the first call, left zero by every call).
+    ``sinks``: as for :func:`attention_generic`."""
     assert partial_o.numel() >= tokens * q_heads * max_splits * head_dim
     assert partial_ml.numel() >= tokens * q_heads * max_splits * 2
     assert counters.numel() >= tokens * kv_heads
+    if sinks is not None:
+        _need(sinks, torch.float32, "sinks")
+        _check(library().celeg_attention_decode_sinks(
+            _ptr(q), q_row_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), _ptr(positions),
+            _ptr(token_span), _ptr(block_table), block_table.stride(0), tokens, q_heads, kv_heads, head_dim,
+            page_tokens, int(window or 0), scale, chunk, max_splits, _ptr(partial_o), _ptr(partial_ml),
+            _ptr(counters), _ptr(error_flag), _ptr(sinks), _stream()))
+        return
     _check(library().celeg_attention_decode(
         _ptr(q), q_row_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), _ptr(positions),
         _ptr(token_span), _ptr(block_table), block_table.stride(0), tokens, q_heads, kv_heads, head_dim,
@@ -282,11 +335,13 @@ def attention_prefill(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_c
                       v_cache: torch.Tensor, positions: torch.Tensor, span_begin: torch.Tensor,
                       block_table: torch.Tensor, tokens: int, spans: int, q_heads: int, kv_heads: int,
                       head_dim: int, page_tokens: int, window: Optional[int], scale: float,
-                      error_flag: torch.Tensor) -> None:
+                      error_flag: torch.Tensor, sinks: Optional[torch.Tensor] = None) -> None:
+    if sinks is not None:
+        _need(sinks, torch.float32, "sinks")
     _check(library().celeg_attention_prefill(
         _ptr(q), q_row_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), _ptr(positions),
         _ptr(span_begin), _ptr(block_table), block_table.stride(0), tokens, spans, q_heads, kv_heads, head_dim,
-        page_tokens, int(window or 0), scale, _ptr(error_flag), _stream()))
+        page_tokens, int(window or 0), scale, _ptr(sinks), _ptr(error_flag), _stream()))
 
 
 def attention_prefill_tcgen05_supported(q_heads: int, kv_heads: int, head_dim: int, page_tokens: int,
@@ -447,3 +502,117 @@ def mark_seen(seen: torch.Tensor, tokens: torch.Tensor, token_span: torch.Tensor
               count: int) -> None:
     _check(library().celeg_mark_seen(_ptr(seen), seen.shape[1], _ptr(tokens), _ptr(token_span), _ptr(span_slot),
                                      count, _stream()))
+
+
+# ------------------------------------------------------- Dynamic Tanh blocks, matrix-state mixers
+def add_dyt(residual: torch.Tensor, delta_a: Optional[torch.Tensor], delta_b: Optional[torch.Tensor], n_rows: int,
+            first: Tuple[torch.Tensor, torch.Tensor, float, torch.Tensor],
+            second: Optional[Tuple[torch.Tensor, torch.Tensor, float, torch.Tensor]] = None,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """x = residual (+ delta_a) (+ delta_b), written back unless ``rows`` gathers; ``first`` and ``second`` are
+    (weight, bias, alpha, out): out = tanh(alpha x) weight + bias in the activation type of ``out``."""
+    _need(residual, torch.float32, "residual")
+    width = residual.shape[-1]
+    w1, b1, alpha1, out1 = first
+    w2, b2, alpha2, out2 = second if second is not None else (None, None, 0.0, None)
+    for delta in (delta_a, delta_b):
+        if delta is not None:
+            assert delta.dtype == out1.dtype and delta.shape[-1] == width
+    _check(library().celeg_add_dyt(_ptr(residual), _ptr(delta_a), _ptr(delta_b), _ptr(rows), n_rows, width,
+                                   int(rows is None), _ptr(w1), _ptr(b1), alpha1, _ptr(out1), _ptr(w2), _ptr(b2), alpha2,
+                                   _ptr(out2), dtype_code(out1.dtype), _stream()))
+
+
+def add_to_residual(residual: torch.Tensor, delta_a: Optional[torch.Tensor], delta_b: Optional[torch.Tensor],
+                    n_rows: int) -> None:
+    """residual[:n_rows] += delta_a (+ delta_b), float32 sums."""
+    _need(residual, torch.float32, "residual")
+    given = delta_a if delta_a is not None else delta_b
+    if given is None:
+        return
+    _check(library().celeg_add_dyt(_ptr(residual), _ptr(delta_a), _ptr(delta_b), None, n_rows, residual.shape[-1], 1,
+                                   None, None, 0.0, None, None, None, 0.0, None, dtype_code(given.dtype), _stream()))
+
+
+def join_stream_embedding(residual: torch.Tensor, delta_a: Optional[torch.Tensor], delta_b: Optional[torch.Tensor],
+                          table: torch.Tensor, tokens: torch.Tensor, joined: torch.Tensor, n_rows: int,
+                          multiplier: float = 1.0) -> None:
+    """joined[t] = [residual[t] (+ deltas) | multiplier * table[tokens[t]]] in the type of ``joined`` (= the table's)."""
+    _need(residual, torch.float32, "residual")
+    _need(tokens, torch.int32, "tokens")
+    width = residual.shape[-1]
+    assert joined.shape[-1] == 2 * width and table.shape[1] == width and table.dtype == joined.dtype
+    _check(library().celeg_join_stream_embedding(_ptr(residual), _ptr(delta_a), _ptr(delta_b), _ptr(table), _ptr(tokens),
+                                                 _ptr(joined), n_rows, width, table.shape[0], multiplier,
+                                                 dtype_code(joined.dtype), _stream()))
+
+
+ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU = 0, 1, 2
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, rows: int, kind: int) -> None:
+    """out[:rows] = act(x[:rows]) element by element (in place allowed); both contiguous, same shape."""
+    assert x.is_contiguous() and out.is_contiguous() and x.shape[1:] == out.shape[1:] and x.dtype == out.dtype
+    _check(library().celeg_activation(_ptr(x), _ptr(out), rows * x.shape[1], kind, dtype_code(x.dtype), _stream()))
+
+
+def softcap(logits: torch.Tensor, rows: int, cap: float) -> None:
+    """logits[:rows] = cap * tanh(logits[:rows] / cap), in place (float32, contiguous)."""
+    _need(logits, torch.float32, "logits")
+    _check(library().celeg_softcap(_ptr(logits), rows * logits.shape[1], cap, _stream()))
+
+
+SCAN_DELTA, SCAN_MLSTM = 0, 1
+SCAN_MAX_DIM = 256
+
+
+def recurrent_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gates: torch.Tensor, out: torch.Tensor,
+                   state: torch.Tensor, slot_stride: int, span_begin: torch.Tensor, span_slot: torch.Tensor, spans: int,
+                   heads: int, kv_heads: int, dim: int, vdim: int, q_scale: float) -> None:
+    """The matrix-state recurrences of csrc/recurrent_scan.cu over the step's spans. q, k, v: float32 column
+    views of [tokens, *] buffers (row strides are taken from them); gates float32 [tokens, 2*heads]; out float32
+    [tokens, heads*vdim]; ``state`` points at this part's floats inside slot 0."""
+    for tensor in (q, k, v, gates, out, state):
+        assert tensor.dtype == torch.float32 and tensor.stride(-1) == 1
+    assert gates.is_contiguous() and out.is_contiguous() and gates.shape[1] == 2 * heads and out.shape[1] == heads * vdim
+    _check(library().celeg_recurrent_scan(mode, _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0),
+                                          _ptr(gates), _ptr(out), _ptr(state), slot_stride, _ptr(span_begin),
+                                          _ptr(span_slot), spans, heads, kv_heads, dim, vdim, q_scale, _stream()))
+
+
+def mlstm_gates(pre_i: torch.Tensor, pre_f: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float,
+                gates: torch.Tensor, tokens: int, heads: int) -> None:
+    """gates[t] = [cap tanh((pre_i + bias_i) / cap) | logsigmoid(cap tanh((pre_f + bias_f) / cap))], float32."""
+    assert pre_i.dtype == torch.float32 and pre_f.dtype == torch.float32 and pre_i.stride(0) == pre_f.stride(0)
+    _check(library().celeg_mlstm_gates(_ptr(pre_i), _ptr(pre_f), pre_i.stride(0), _ptr(bias_i), _ptr(bias_f), cap,
+                                       _ptr(gates), tokens, heads, _stream()))
+
+
+def delta_prepare(proj: torch.Tensor, kernel: torch.Tensor, carried: torch.Tensor, slot_stride: int,
+                  token_span: torch.Tensor, span_begin: torch.Tensor, span_slot: torch.Tensor, conv_out: torch.Tensor,
+                  pre_beta: torch.Tensor, pre_a: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                  gates: torch.Tensor, tokens: int, spans: int, channels: int, taps: int, qk_heads: int, dim: int,
+                  heads: int, unit_eps: float) -> None:
+    """The gated delta rule's token-parallel part: short causal convolutions (carried inputs before a span's
+    start) with SiLU over the first ``channels`` columns of ``proj`` ([q | k | v]), unit q and k heads, beta and
+    decay; then the carried inputs are moved on (a second launch). All float32."""
+    assert proj.dtype == torch.float32 and conv_out.dtype == torch.float32 and conv_out.shape[1] == channels
+    assert pre_beta.stride(0) == proj.stride(0) and pre_a.stride(0) == proj.stride(0)
+    _check(library().celeg_delta_prepare(_ptr(proj), proj.stride(0), _ptr(kernel), _ptr(carried), slot_stride,
+                                         _ptr(token_span), _ptr(span_begin), _ptr(span_slot), _ptr(conv_out),
+                                         _ptr(pre_beta), _ptr(pre_a), _ptr(a_log), _ptr(dt_bias), _ptr(gates), tokens,
+                                         spans, channels, taps, qk_heads, dim, heads, unit_eps, _stream()))
+    global LAUNCHES
+    LAUNCHES += 1 if taps > 1 else 0
+
+
+GATE_SIGMOID, GATE_SILU = 0, 1
+
+
+def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, weight_per_head: bool, out: torch.Tensor,
+                    tokens: int, heads: int, vdim: int, eps: float, gate_kind: int) -> None:
+    """out = o / sqrt(mean_head(o^2) + eps) * weight * act(gate) per (token, head); o and gate float32."""
+    assert o.dtype == torch.float32 and gate.dtype == torch.float32 and o.is_contiguous() and gate.stride(-1) == 1
+    _check(library().celeg_gated_head_norm(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), int(weight_per_head),
+                                           _ptr(out), tokens, heads, vdim, eps, gate_kind, dtype_code(out.dtype),
+                                           _stream()))

@@ -55,3 +55,35 @@ class PreNormResidual:
         between = self.ffn_norm if takes is not None and takes(step) else None
         self._sublayer(self.mixer_norm, self.mixer, self.delta_a, between, stream, step)
         self._sublayer(self.ffn_norm, self.ffn, self.delta_b, after, stream, step)
+
+
+@register_part("arrangement", "parallel_residual")
+class ParallelResidual:
+    """y = x + Mixer(Norm_1(x)) + FeedForward(Norm_2(x)): both read the same x, each through its own norm, and
+    both outputs are owed to the stream together (added inside the next block's norm pass). Without a
+    feed-forward: y = x + Mixer(Norm_1(x))."""
+
+    def __init__(self, layer_parts: Mapping, rt: Runtime):
+        self.rt = rt
+        self.mixer_norm = layer_parts["mixer_norm"]
+        self.mixer = layer_parts["mixer"]
+        self.ffn_norm = layer_parts.get("feed_forward_norm")
+        self.ffn = layer_parts.get("feed_forward")
+        hidden = self.mixer_norm.width
+        self.normed_a = rt.scratch("block.normed", hidden)
+        self.normed_b = rt.scratch("block.normed_b", hidden)
+        self.delta_a = rt.scratch("block.delta_a", hidden)
+        self.delta_b = rt.scratch("block.delta_b", hidden)
+
+    def run(self, stream: ResidualStream, step: StepContext) -> None:
+        stream.expect(self.delta_a, None, step.tokens)
+        if self.ffn is None:
+            x = stream.normed(self.mixer_norm, self.normed_a, step.tokens)
+            self.mixer.forward(x, self.delta_a, step)
+            stream.add_later(self.delta_a)
+            return
+        x_mixer, x_ffn = stream.normed_pair(self.mixer_norm, self.normed_a, self.ffn_norm, self.normed_b, step.tokens)
+        self.mixer.forward(x_mixer, self.delta_a, step)
+        self.ffn.forward(x_ffn, self.delta_b, step)
+        stream.add_later(self.delta_a)
+        stream.add_later_beside(self.delta_b)

@@ -49,13 +49,16 @@ class EmbeddingInput:
 @register_part("output", "norm_head")
 class NormHeadOutput:
     """logits = multiplier * (norm(stream rows) @ head^T): the nested part ``norm``, then the head matrix
-    (the embedding table itself when the description ties them: the runtime places a tensor once)."""
+    (the embedding table itself when the description ties them: the runtime places a tensor once); with
+    ``softcap`` the logits are then capped smoothly: cap * tanh(logits / cap)."""
 
     def __init__(self, params: Mapping, weights: Mapping[str, torch.Tensor], parts: Mapping, rt: Runtime):
         self.rt = rt
         self.norm = parts["norm"]
         self.head = rt.matrix(weights["head"])
         self.multiplier = float(params.get("multiplier", 1.0))
+        cap = params.get("softcap")
+        self.softcap = float(cap) if cap else None        # logits <- cap * tanh(logits / cap)
         self.normed = rt.scratch("model.final_normed", int(self.head.shape[1]))
 
     def next_norm(self, step: StepContext, n_logits: int):
@@ -71,3 +74,5 @@ class NormHeadOutput:
         self.rt.linear(normed, self.head, logits, n_logits)
         if self.multiplier != 1.0:
             logits[:n_logits].mul_(self.multiplier)
+        if self.softcap is not None:
+            kernels.softcap(logits, n_logits, self.softcap)

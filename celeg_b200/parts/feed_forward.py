@@ -39,3 +39,31 @@ class SwiGluFeedForward:
         rt, t = self.rt, step.tokens
         rt.linear_swiglu(x, self.w_gate_up, self.gate_up, self.activated, t, self.inner)
         rt.linear(self.activated, self.w_down, out, t)
+
+
+@register_part("feed_forward", "dense")
+class DenseFeedForward:
+    """down(act(up(x))) with act one of ``gelu`` (exact, by erf), ``gelu_tanh`` or ``silu``; the activation in
+    float32, rounded once."""
+
+    ACTIVATIONS = {"gelu": kernels.ACT_GELU_ERF, "gelu_tanh": kernels.ACT_GELU_TANH, "silu": kernels.ACT_SILU}
+
+    def __init__(self, params: Mapping, weights: Mapping[str, torch.Tensor], parts: Mapping, rt: Runtime):
+        self.rt = rt
+        self.hidden = int(params["hidden_size"])
+        self.inner = int(params["intermediate_size"])
+        name = params.get("activation", "gelu")
+        if name not in self.ACTIVATIONS:
+            raise ValueError(f"dense feed-forward: unknown activation {name!r}; known: {', '.join(self.ACTIVATIONS)}")
+        self.activation = self.ACTIVATIONS[name]
+        self.w_up = rt.matrix(weights["up"])
+        self.w_down = rt.matrix(weights["down"])
+        self.raised = rt.scratch("dense.up", self.inner)
+
+    ends_with_product = True      # forward() writes `out` last, with rt.linear
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
+        rt, t = self.rt, step.tokens
+        rt.linear(x, self.w_up, self.raised, t)
+        kernels.activation(self.raised, self.raised, t, self.activation)
+        rt.linear(self.raised, self.w_down, out, t)

@@ -105,8 +105,10 @@ def decode_split(tokens: int, kv_heads: int, context_bucket: int, window: Option
 
 @register_part("mixer", "attention")
 class AttentionMixer:
-    """Causal grouped-query attention over the paged cache with optional per-head q/k RMSNorm,
-    a position encoding, an optional window, and softmax scale given by the configuration.
+    """Causal grouped-query attention over the paged cache with optional per-head q/k RMSNorm (or one over
+    the whole projection: ``whole_qk_norm``), a position encoding, an optional window, an optional sink per
+    query head, values that are the unrotated keys (``values_are_keys``: no value projection), and softmax
+    scale given by the configuration.
     Order of operations as in celeg (src/backend/cpu/operators/attention_token.cpp:151-204;
     src/backend/cuda/packed/operators.cu:66-99, 101-246, 494-529): fused q|k|v projection,
     norm, rotation, cache write, attention, output projection."""
@@ -121,6 +123,12 @@ class AttentionMixer:
         self.scale = float(params.get("softmax_scale", self.head_dim ** -0.5))
         self.eps = float(params.get("qk_norm_eps", 1e-6))
         self.reads_only = bool(params.get("reads_cache_only", False))
+        # q and k normalised over the whole projection (weights as wide as the projections) instead of per head
+        self.whole_qk_norm = bool(params.get("whole_qk_norm", False))
+        # no value projection: a key as projected (before norm and rotation) is its own value
+        self.values_are_keys = bool(params.get("values_are_keys", False))
+        if (self.whole_qk_norm or self.values_are_keys) and self.reads_only:
+            raise ValueError("whole_qk_norm and values_are_keys are for mixers that own their cache")
         if self.heads % self.kv_heads:
             raise ValueError(f"{self.heads} query heads are not a multiple of {self.kv_heads} kv heads")
         self.position = parts.get("position")
@@ -129,14 +137,25 @@ class AttentionMixer:
         if self.reads_only:
             self.stored_kv_heads = 0
             fused = weights["q_proj"]
+        elif self.values_are_keys:
+            self.stored_kv_heads = self.kv_heads
+            fused = torch.cat([weights["q_proj"], weights["k_proj"]], dim=0)
         else:
             self.stored_kv_heads = self.kv_heads
             fused = torch.cat([weights["q_proj"], weights["k_proj"], weights["v_proj"]], dim=0)
-        self.qkv_width = q_width + 2 * self.stored_kv_heads * self.head_dim
+        self.qkv_width = q_width + (1 if self.values_are_keys else 2) * self.stored_kv_heads * self.head_dim
         self.w_qkv = rt.matrix(fused)
         self.w_out = rt.matrix(weights["out_proj"])
         self.q_norm = rt.vector(weights["q_norm"]) if "q_norm" in weights else None
         self.k_norm = rt.vector(weights["k_norm"]) if "k_norm" in weights else None
+        # a learned score per query head that enters the softmax's denominator once: no key, no value, not scaled
+        self.sinks = rt.vector(weights["sinks"]) if "sinks" in weights else None
+        if self.sinks is not None and self.sinks.shape != (self.heads,):
+            raise ValueError(f"attention sinks have shape {tuple(self.sinks.shape)}, expected ({self.heads},)")
+        if self.values_are_keys and not self.whole_qk_norm and (self.q_norm is not None or self.k_norm is not None):
+            raise ValueError("values_are_keys with per-head q/k norms is not built; use whole_qk_norm or no norms")
+        self.row_scales = (rt.flat_scratch("attention.row_scales", 2 * rt.max_tokens, torch.float32)
+                           if self.whole_qk_norm or self.values_are_keys else None)
         self.binding: Optional[PagedBinding] = None
         self._resident_blocks: Optional[int] = None      # (asked of the kernel library at the first decode step)
         self.qkv = rt.scratch("attention.qkv", self.qkv_width)
@@ -162,7 +181,18 @@ class AttentionMixer:
         table = step.block_tables[b.group]
         fused = self.position.fused() if self.position is not None else {"inv_freq": None, "rotary_dim": 0}
         store = b.owner and not self.reads_only
-        if (fused is not None and store and rt.fuse_decode_qk and self._decodes(step)):
+        if self.whole_qk_norm or self.values_are_keys:
+            if fused is None or not store:
+                raise ValueError("whole_qk_norm / values_are_keys need a position part with fused() tables and a "
+                                 "cache of the mixer's own")
+            kernels.qk_whole_norm_rope_store(self.qkv, self.q_norm, self.k_norm, fused["inv_freq"], step.positions,
+                                             step.token_span, table, b.k, b.v, t, self.heads, self.kv_heads,
+                                             self.head_dim, fused["rotary_dim"], b.page_tokens, self.eps,
+                                             self.values_are_keys, self.row_scales, step.error_flag)
+            self.attend(step, table)
+            rt.linear(self.attended, self.w_out, out, t)
+            return
+        if (fused is not None and store and rt.fuse_decode_qk and self.sinks is None and self._decodes(step)):
             # one token per request: norm, rotation and cache write happen inside the attention kernel
             chunk, max_splits, partial_o, partial_ml, counters = self._decode_split(step)
             kernels.attention_decode_fused(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
@@ -242,7 +272,7 @@ class AttentionMixer:
         kernels.attention_decode(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
                                  step.token_span, table, count, self.heads, self.kv_heads,
                                  self.head_dim, b.page_tokens, self.window, self.scale, chunk, max_splits,
-                                 partial_o, partial_ml, counters, step.error_flag)
+                                 partial_o, partial_ml, counters, step.error_flag, sinks=self.sinks)
 
     def _attend_portions(self, step: StepContext, table: torch.Tensor, skip: int) -> None:
         """The spans from ``skip`` on (the spans before it have one token each, so span ``skip`` begins at token
@@ -254,7 +284,8 @@ class AttentionMixer:
         span_begin = step.span_begin[skip:]
         span_table = table[skip:]
         lengths = step.host_span_lengths[skip:] if step.host_span_lengths is not None else None
-        if (lengths is not None and rt.tcgen05_attention and kernels.attention_prefill_tcgen05_supported(
+        if (lengths is not None and rt.tcgen05_attention and self.sinks is None
+                and kernels.attention_prefill_tcgen05_supported(
                 self.heads, self.kv_heads, self.head_dim, b.page_tokens, rt.act_dtype)):
             # head size 64: S and O' in tensor memory, Q/K/V by TMA
             tiles = step.prompt_tile_bound or sum((length + 127) // 128 for length in lengths)
@@ -266,12 +297,13 @@ class AttentionMixer:
         if kernels.attention_prefill_supported(self.heads, self.kv_heads, self.head_dim, rt.act_dtype):
             kernels.attention_prefill(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
                                       span_begin, span_table, step.tokens, spans, self.heads, self.kv_heads,
-                                      self.head_dim, b.page_tokens, self.window, self.scale, step.error_flag)
+                                      self.head_dim, b.page_tokens, self.window, self.scale, step.error_flag,
+                                      sinks=self.sinks)
             return
         kernels.attention_generic(self.qkv[skip:], self.qkv_width, self.attended[skip:], b.k, b.v,
                                   step.positions[skip:], step.token_span[skip:], table, step.tokens - skip,
                                   self.heads, self.kv_heads, self.head_dim, b.page_tokens, self.window, self.scale,
-                                  step.error_flag)
+                                  step.error_flag, sinks=self.sinks)
 
 
 @register_part("mixer", "short_conv")

@@ -9,6 +9,7 @@ Keys are cached after encoding, so an encoding must be a pure function of the ab
 """
 from __future__ import annotations
 
+import math
 from typing import Mapping, Optional
 
 import torch
@@ -22,7 +23,8 @@ class SplitHalfRope:
     """Rotary embedding over pairs (i, i + rotary/2): angle = position * theta^(-2i/rotary).
     Frequencies are computed in double and rounded to float32, the angle product and
     sin/cos are float32, as celeg's CPU kernel does (src/backend/cpu/kernels/rope.cpp:74-79;
-    include/celeg/model/position.hpp:77-78)."""
+    include/celeg/model/position.hpp:77-78). ``wavelength_scaling`` = {factor, low, high, original}
+    rescales the frequencies (:func:`scale_by_wavelength`)."""
 
     def __init__(self, params: Mapping, rt: Runtime):
         self.theta = float(params["theta"])
@@ -32,11 +34,30 @@ class SplitHalfRope:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
         half = self.rotary_dim // 2
         exponents = torch.arange(half, dtype=torch.float64) * (-2.0 / self.rotary_dim)
-        self.inv_freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), exponents).to(
-            torch.float32).to(rt.device)
+        frequencies = torch.pow(torch.tensor(self.theta, dtype=torch.float64), exponents)
+        scaling = params.get("wavelength_scaling")
+        if scaling:
+            frequencies = scale_by_wavelength(frequencies, float(scaling["factor"]), float(scaling["low"]),
+                                              float(scaling["high"]), float(scaling["original"]))
+        self.inv_freq = frequencies.to(torch.float32).to(rt.device)
 
     def fused(self) -> Optional[dict]:
         return {"inv_freq": self.inv_freq, "rotary_dim": self.rotary_dim}
+
+
+def scale_by_wavelength(frequencies: torch.Tensor, factor: float, low: float, high: float,
+                        original: float) -> torch.Tensor:
+    """Context extension by wavelength (the rule Llama 3.1 checkpoints state in ``rope_scaling``): a frequency
+    whose wavelength 2 pi / f is shorter than original / high stays, one longer than original / low is divided
+    by ``factor``, and between the two the frequency is (1 - s) f / factor + s f with
+    s = (original / wavelength - low) / (high - low). In double, like the frequencies themselves."""
+    if factor <= 0 or high <= low or original <= 0:
+        raise ValueError("wavelength scaling needs factor > 0, high > low and original > 0")
+    wavelength = 2.0 * math.pi / frequencies
+    smooth = (original / wavelength - low) / (high - low)
+    blended = (1.0 - smooth) * frequencies / factor + smooth * frequencies
+    return torch.where(wavelength < original / high, frequencies,
+                       torch.where(wavelength > original / low, frequencies / factor, blended))
 
 
 @register_part("position", "none")

@@ -1,0 +1,165 @@
+"""Mixers whose cache is a matrix per head that every token rewrites (kernels: csrc/recurrent_scan.cu).
+The state is float32 on both precision paths and lives in the request's state slot; gates, unit norms,
+decays and every sum of the recurrence are float32; the projections run in the path's matrix type and leave
+float32 results.
+
+    mlstm         S' = a S + b k v^T, n' = a n + b k with exponential gates kept in range by a running maximum;
+                  read-out S'^T q over max(|n'.q|, exp(-m')) (Beck et al., "xLSTM: Extended Long Short-Term
+                  Memory", 2024, the matrix-memory cell)
+    gated_delta   S' = g S + k (beta (v - (g S)^T k))^T, read-out S'^T q, after short causal convolutions with
+                  SiLU on q, k, v and unit-length q, k (Yang, Kautz, Hatamizadeh, "Gated Delta Networks:
+                  Improving Mamba2 with Delta Rule", 2024)
+"""
+from __future__ import annotations
+
+from typing import Mapping, Optional
+
+import torch
+
+from .. import kernels
+from ..cache.manager import StateNeed
+from .mixers import StateBinding
+from .registry import register_part
+from .runtime import Runtime, StepContext
+
+
+@register_part("mixer", "mlstm")
+class MlstmMixer:
+    """q = W_q x / sqrt(dim), k = W_k x (heads x dim), v = W_v x (heads x vdim); per head a log input gate
+    cap tanh((W_i x + b_i) / cap) and a log forget gate logsigmoid(cap tanh((W_f x + b_f) / cap)). Each head's
+    read-out is divided by its root mean square, scaled by ``norm`` (all heads' width), gated by sigmoid(W_g x)
+    and projected by W_o. The running maximum of a new request is 0."""
+
+    def __init__(self, params: Mapping, weights: Mapping[str, torch.Tensor], parts: Mapping, rt: Runtime):
+        self.rt = rt
+        self.hidden = int(params["hidden_size"])
+        self.heads = int(params["heads"])
+        self.dim = int(params["dim"])
+        self.vdim = int(params["vdim"])
+        self.cap = float(params["gate_cap"])
+        self.eps = float(params["eps"])
+        if self.dim > kernels.SCAN_MAX_DIM:
+            raise ValueError(f"mlstm: a key size of {self.dim} exceeds {kernels.SCAN_MAX_DIM}")
+        self.qk_width = self.heads * self.dim
+        self.v_width = self.heads * self.vdim
+        fused = torch.cat([weights["q"], weights["k"], weights["v"], weights["gate"], weights["input_gate"],
+                           weights["forget_gate"]], dim=0)
+        self.w_in = rt.matrix(fused)
+        self.w_out = rt.matrix(weights["out"])
+        self.bias_i = rt.vector(weights["input_gate_bias"])
+        self.bias_f = rt.vector(weights["forget_gate_bias"])
+        self.norm = rt.vector(weights["norm"])
+        self.proj_width = int(fused.shape[0])
+        self.binding: Optional[StateBinding] = None
+        self.projected = rt.scratch("recurrent.proj", self.proj_width, torch.float32)
+        self.gates = rt.scratch("recurrent.gates", 2 * self.heads, torch.float32)
+        self.read = rt.scratch("recurrent.read", self.v_width, torch.float32)
+        self.gated = rt.scratch("recurrent.gated", self.v_width)
+
+    def cache_need(self):
+        return StateNeed(elements=self.heads * self.dim * self.vdim + self.heads * self.dim + self.heads)
+
+    def bind_cache(self, binding: StateBinding) -> None:
+        self.binding = binding
+
+    ends_with_product = True      # forward() writes `out` last, with rt.linear
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
+        rt, t, b = self.rt, step.tokens, self.binding
+        rt.linear(x, self.w_in, self.projected, t)
+        rows = self.projected
+        at = 0
+        q = rows[:, at:at + self.qk_width]; at += self.qk_width
+        k = rows[:, at:at + self.qk_width]; at += self.qk_width
+        v = rows[:, at:at + self.v_width]; at += self.v_width
+        gate = rows[:, at:at + self.v_width]; at += self.v_width
+        pre_i = rows[:, at:at + self.heads]; at += self.heads
+        pre_f = rows[:, at:at + self.heads]
+        kernels.mlstm_gates(pre_i, pre_f, self.bias_i, self.bias_f, self.cap, self.gates, t, self.heads)
+        kernels.recurrent_scan(kernels.SCAN_MLSTM, q, k, v, self.gates, self.read, b.state, b.slot_stride,
+                               step.span_begin, step.span_slot, step.spans, self.heads, self.heads, self.dim,
+                               self.vdim, self.dim ** -0.5)
+        kernels.gated_head_norm(self.read, gate, self.norm, True, self.gated, t, self.heads, self.vdim, self.eps,
+                                kernels.GATE_SIGMOID)
+        rt.linear(self.gated, self.w_out, out, t)
+
+
+@register_part("mixer", "gated_delta")
+class GatedDeltaMixer:
+    """q = W_q x, k = W_k x (kv_heads x dim), v = W_v x (heads x vdim), each through a depthwise causal
+    convolution of ``taps`` taps and SiLU; q and k per head divided by sqrt(sum of squares + 1e-6), q also by
+    sqrt(dim); beta = sigmoid(W_b x) and decay g = exp(-exp(A_log) softplus(W_a x + dt_bias)) per head. Head h
+    reads q/k head h // (heads / kv_heads). Each head's read-out is divided by its root mean square, scaled by
+    ``norm`` (vdim, shared by the heads), gated by SiLU(W_g x) and projected by W_o. Per-request state: S per
+    head, then the last taps - 1 inputs of the convolutions."""
+
+    UNIT_EPS = 1e-6
+
+    def __init__(self, params: Mapping, weights: Mapping[str, torch.Tensor], parts: Mapping, rt: Runtime):
+        self.rt = rt
+        self.hidden = int(params["hidden_size"])
+        self.heads = int(params["heads"])
+        self.kv_heads = int(params["kv_heads"])
+        self.dim = int(params["dim"])
+        self.vdim = int(params["vdim"])
+        self.taps = int(params["taps"])
+        self.eps = float(params["eps"])
+        if self.heads % self.kv_heads:
+            raise ValueError(f"gated_delta: {self.heads} heads are not a multiple of {self.kv_heads} q/k heads")
+        if self.dim > kernels.SCAN_MAX_DIM or not 1 <= self.taps <= 16:
+            raise ValueError(f"gated_delta: key size {self.dim} (at most {kernels.SCAN_MAX_DIM}) or {self.taps} taps "
+                             f"(1 to 16) is out of range")
+        self.qk_width = self.kv_heads * self.dim
+        self.v_width = self.heads * self.vdim
+        self.channels = 2 * self.qk_width + self.v_width
+        fused = torch.cat([weights["q"], weights["k"], weights["v"], weights["gate"], weights["beta"],
+                           weights["decay"]], dim=0)
+        self.w_in = rt.matrix(fused)
+        self.w_out = rt.matrix(weights["out"])
+        self.kernel = rt.vector(torch.cat([weights["q_conv"].reshape(self.qk_width, self.taps),
+                                           weights["k_conv"].reshape(self.qk_width, self.taps),
+                                           weights["v_conv"].reshape(self.v_width, self.taps)], dim=0))
+        self.a_log = rt.vector(weights["a_log"])
+        self.dt_bias = rt.vector(weights["dt_bias"])
+        self.norm = rt.vector(weights["norm"])
+        self.proj_width = int(fused.shape[0])
+        self.state_elements = self.heads * self.dim * self.vdim
+        self.binding: Optional[StateBinding] = None
+        self.carried: Optional[torch.Tensor] = None
+        self.projected = rt.scratch("recurrent.proj", self.proj_width, torch.float32)
+        self.convolved = rt.scratch("recurrent.conv", self.channels, torch.float32)
+        self.gates = rt.scratch("recurrent.gates", 2 * self.heads, torch.float32)
+        self.read = rt.scratch("recurrent.read", self.v_width, torch.float32)
+        self.gated = rt.scratch("recurrent.gated", self.v_width)
+
+    def cache_need(self):
+        return StateNeed(elements=self.state_elements + (self.taps - 1) * self.channels)
+
+    def bind_cache(self, binding: StateBinding) -> None:
+        self.binding = binding
+        self.carried = binding.state[:, self.state_elements:]
+
+    ends_with_product = True      # forward() writes `out` last, with rt.linear
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
+        rt, t, b = self.rt, step.tokens, self.binding
+        rt.linear(x, self.w_in, self.projected, t)
+        rows = self.projected
+        at = self.channels
+        gate = rows[:, at:at + self.v_width]; at += self.v_width
+        pre_beta = rows[:, at:at + self.heads]; at += self.heads
+        pre_a = rows[:, at:at + self.heads]
+        kernels.delta_prepare(rows, self.kernel, self.carried, b.slot_stride, step.token_span, step.span_begin,
+                              step.span_slot, self.convolved, pre_beta, pre_a, self.a_log, self.dt_bias, self.gates,
+                              t, step.spans, self.channels, self.taps, self.kv_heads, self.dim, self.heads,
+                              self.UNIT_EPS)
+        conv = self.convolved
+        q = conv[:, :self.qk_width]
+        k = conv[:, self.qk_width:2 * self.qk_width]
+        v = conv[:, 2 * self.qk_width:]
+        kernels.recurrent_scan(kernels.SCAN_DELTA, q, k, v, self.gates, self.read, b.state, b.slot_stride,
+                               step.span_begin, step.span_slot, step.spans, self.heads, self.kv_heads, self.dim,
+                               self.vdim, self.dim ** -0.5)
+        kernels.gated_head_norm(self.read, gate, self.norm, False, self.gated, t, self.heads, self.vdim, self.eps,
+                                kernels.GATE_SILU)
+        rt.linear(self.gated, self.w_out, out, t)

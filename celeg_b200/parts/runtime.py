@@ -37,6 +37,8 @@ class ResidualStream:
         self.hidden = hidden
         self.residual = rt.scratch("stream.residual", hidden, torch.float32)
         self.pending: Optional[torch.Tensor] = None
+        self.pending_b: Optional[torch.Tensor] = None    # a second output owed to the stream (blocks whose mixer and
+                                                         # feed-forward sit side by side); only beside ``pending``
         self.prepared = None                    # (norm, SplitNorm) left by the last product
         self.after_layer = None                 # the norm after the layer being run, if its reader takes a split norm
         self.pieces = (hidden + 15) // 16
@@ -46,6 +48,7 @@ class ResidualStream:
 
     def begin(self) -> None:
         self.pending = None
+        self.pending_b = None
         self.prepared = None
         self.after_layer = None
         self.rt.sink = None
@@ -68,10 +71,37 @@ class ResidualStream:
             if prepared_norm is norm and gather is None:
                 return split
             raise RuntimeError("a norm was prepared for another reader than the one that asks")
-        norm.add_norm(self.residual, self.pending, out, rows, rows=gather)
+        if self.pending_b is not None and not getattr(norm, "adds_two", False):
+            if gather is not None:
+                raise RuntimeError("two outputs are owed to the stream and the norm that gathers rows adds one")
+            self.settle(rows)
+        if self.pending_b is not None:
+            norm.add_norm(self.residual, self.pending, out, rows, rows=gather, delta_b=self.pending_b)
+        else:
+            norm.add_norm(self.residual, self.pending, out, rows, rows=gather)
         if gather is None:
-            self.pending = None
+            self.pending = self.pending_b = None
         return out
+
+    def normed_pair(self, norm_a, out_a: torch.Tensor, norm_b, out_b: torch.Tensor, rows: int):
+        """(norm_a(x), norm_b(x)) of the same x = stream + what is owed to it, which is added for good. Norms that
+        can (``add_norm_pair``) do both in the pass that adds; others run one after the other."""
+        if self.prepared is not None:
+            raise RuntimeError("a norm was prepared for another reader than the pair that asks")
+        pair = getattr(norm_a, "add_norm_pair", None)
+        if pair is not None and type(norm_a) is type(norm_b):
+            pair(self.residual, self.pending, self.pending_b, norm_b, out_a, out_b, rows)
+            self.pending = self.pending_b = None
+            return out_a, out_b
+        self.normed(norm_a, out_a, rows)
+        norm_b.add_norm(self.residual, None, out_b, rows)
+        return out_a, out_b
+
+    def settle(self, rows: int) -> None:
+        """Add what is owed to the stream now (for a reader that wants the stream itself)."""
+        if self.pending is not None or self.pending_b is not None:
+            kernels.add_to_residual(self.residual, self.pending, self.pending_b, rows)
+            self.pending = self.pending_b = None
 
     def expect(self, buffer: torch.Tensor, upcoming, rows: int) -> None:
         """A part is about to write its output to ``buffer``; ``upcoming`` is the norm that reads the
@@ -91,6 +121,12 @@ class ResidualStream:
             self.prepared = (sink.norm, sink.split)          # the product has added to the stream already
             return
         self.pending = delta
+
+    def add_later_beside(self, delta: torch.Tensor) -> None:
+        """A second output of the same block, owed to the stream beside the one of :meth:`add_later`."""
+        if self.pending is None or self.pending_b is not None or self.prepared is not None:
+            raise RuntimeError("a second output is owed to the stream only beside a first one")
+        self.pending_b = delta
 
 
 class Runtime:

@@ -16,7 +16,9 @@ import torch
 from ..config.registry import Architecture, architecture_of
 from .safetensors_io import write_safetensors
 
-_DISTRIBUTIONS = {"linear": (0.0, 0.02), "norm": (1.0, 0.05), "conv": (0.0, 0.1)}
+# (mean, standard deviation); "fan_in": N(0, 1 / columns), which keeps activations of order one at any width
+_DISTRIBUTIONS = {"linear": (0.0, 0.02), "norm": (1.0, 0.05), "conv": (0.0, 0.1), "small": (0.0, 0.3),
+                  "alpha": (0.7, 0.05), "taps": (0.0, 0.5), "fan_in": (0.0, None)}
 
 
 def _generator(seed: int, name: str) -> torch.Generator:
@@ -35,6 +37,8 @@ def random_tensors(architecture: Architecture, config: Any, seed: int,
             continue
         mean, std = _DISTRIBUTIONS[architecture.random_init(config, ref.name, ref.shape)]
         shape = ref.alt_shapes[0] if ref.alt_shapes else ref.shape   # stored layout of the checkpoint
+        if std is None:
+            std = float(shape[-1]) ** -0.5
         values = torch.empty(shape, dtype=torch.float32).normal_(0.0, std, generator=_generator(seed, ref.name))
         tensors[ref.name] = (values + mean).to(dtype)
     return tensors
