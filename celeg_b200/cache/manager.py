@@ -26,6 +26,7 @@ import numpy as np
 from .pages import OutOfPages, PageError, PagePool
 
 NO_PAGE = -1
+NO_PAGE_LIMIT = 1 << 62        # positions that fit when nothing is paged
 
 
 @dataclass(frozen=True)
@@ -235,6 +236,8 @@ class CacheManager:
                              tables=[[] for _ in self.groups],
                              first_live_page=[0 for _ in self.groups],
                              arrays=arrays, page_tokens=self.page_tokens)
+        if not self.groups:
+            cache.capacity = NO_PAGE_LIMIT      # a model without paged mixers: a request never outgrows its pages
         self._live[request_id] = cache
         return cache
 

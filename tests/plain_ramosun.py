@@ -98,7 +98,7 @@ def attention_mixer(h: np.ndarray, tensors, prefix: str, mixer: dict, eps: float
     """Windowed attention with a sink; the values are the keys as projected (before norm and rotation)."""
     tokens = h.shape[0]
     heads, kv_heads, dim = int(mixer["heads"]), int(mixer["kv_heads"]), int(mixer["dim"])
-    window = int(mixer["mask"]["size"])
+    window = int(mixer["mask"]["size"]) if mixer.get("mask") else tokens        # no mask: every earlier token
     scale = float(mixer["scale"])
     q = h @ tensors[prefix + "q"].T
     k = h @ tensors[prefix + "k"].T
