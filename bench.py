@@ -8,6 +8,8 @@ batch 1 and 64. Prints ONE JSON line.
                   [--prefill-tokens T] [--chunk C] [--kernel-times] [--no-cuda-graph]      one phase, a short record
   python bench.py --workload lfm2-700m|lfm2-350m [--requests N] [--new-tokens N] [--max-batched-tokens N]
                   [--prefill-chunk N] [--kernel-times]       a scheduler workload through Engine.submit/step/poll
+  python bench.py --design ramosun [--design-size w1024|w2048] [--kernel-times]
+                  the Ramosun design beside the closest LFM2 model at equal size: prefill of 2,048 tokens, decode at batch 8
 
 A "step" is one decode step of the whole batch. ``value`` is timed on the device (CUDA events
 around K steps of step function + sampling kernel, synthetic token ids); ``e2e`` is the same
@@ -190,7 +192,9 @@ class KernelTimer:
     (``--no-cuda-graph``); the numbers include what a launch from the host adds, so read them as shares."""
     NAMES = ("embedding", "add_rmsnorm", "short_conv", "qk_norm_rope_store", "attention_generic", "attention_decode",
              "attention_decode_fused", "attention_prefill", "attention_prefill_tcgen05", "gemv_bf16", "gemm_tcgen05",
-             "gemm_stream", "gemm_f32", "swiglu", "sample", "sample_greedy", "mark_seen")
+             "gemm_stream", "gemm_f32", "swiglu", "sample", "sample_greedy", "mark_seen",
+             "add_dyt", "add_to_residual", "join_stream_embedding", "activation", "softcap", "recurrent_scan",
+             "mlstm_gates", "delta_prepare", "gated_head_norm", "qk_whole_norm_rope_store")
 
     def __init__(self):
         self.pairs = []
@@ -450,6 +454,81 @@ def run_ours(args) -> dict:
     }
 
 
+# --design ramosun: the Ramosun design at sizes that resemble a real model's layers, beside an LFM2 model of the same
+# width, depth, vocabulary and about the same number of parameters (its closest relative here: fixed-state mixers
+# beside attention). Eight layers each, heads of 64.
+DESIGN_SIZES = {"w1024": (1024, 16384), "w2048": (2048, 32768)}
+
+
+def ramosun_config(width: int, vocab: int) -> dict:
+    heads = width // 64
+    ff = {"kind": "dense", "ff": 4 * width}
+    scaling = {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}
+    attention = {"type": "attention", "mlp": ff, "mixer": {
+        "heads": heads, "kv_heads": heads // 4, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 1024},
+        "rot": {"base": 1000000.0, "dims": 64, "scaling": scaling}}}
+    mlstm = {"type": "mlstm", "mlp": ff, "mixer": {"heads": heads // 2, "dim": 64, "vdim": 128, "gate_cap": 15.0}}
+    delta = {"type": "delta", "mlp": ff, "mixer": {"heads": heads, "kv_heads": heads // 2, "dim": 64, "vdim": 64, "conv": 4}}
+    return {"architecture": "Ramosun", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "layers": [attention, mlstm, delta, attention, mlstm, delta], "loop": {"start": 1, "stop": 3, "times": 2},
+            "max_context": 8192}
+
+
+def lfm2_relative(width: int, vocab: int) -> dict:
+    raw = dict(LFM2_1P2B)
+    # eight blocks like Ramosun's run order; a SwiGLU of 8/3 width has the parameters of a dense feed-forward of 4 width
+    raw.update({"vocab_size": vocab, "hidden_size": width, "num_hidden_layers": 8, "num_attention_heads": width // 64,
+                "num_key_value_heads": width // 256, "intermediate_size": (8 * width // 3 + 127) // 128 * 128,
+                "max_position_embeddings": 8192,
+                "layer_types": ["full_attention", "conv", "conv", "conv", "conv", "full_attention", "conv", "conv"]})
+    return raw
+
+
+def run_design(args) -> dict:
+    """Prefill of 2,048 tokens and decoding at batch 8 (512-token prompts) for both models at every size, on the
+    device; and with ``--kernel-times`` the device time per kind of kernel in steps launched kernel by kernel."""
+    import torch
+    from celeg_b200 import Engine, EngineOptions, KernelOptions
+    from celeg_b200.sampling import Sampler
+    peak, peak_source = peaks()
+    record = {"design": args.design, "peaks": peak, "of": peak_source, "sizes": {}}
+    for tag, (width, vocab) in DESIGN_SIZES.items():
+        if args.design_size and tag != args.design_size:
+            continue
+        entry = {}
+        for name, raw in (("ramosun", ramosun_config(width, vocab)), ("lfm2", lfm2_relative(width, vocab))):
+            folder = model_folder(raw)
+            options = EngineOptions(max_active_requests=8, max_batched_tokens=PREFILL_TOKENS,
+                                    prefill_chunk_tokens=PREFILL_TOKENS, page_tokens=args.page_tokens,
+                                    logical_kv_pages=8 * (-(-CONTEXT // args.page_tokens)))
+            engine = Engine(folder, max_context=CONTEXT, dtype="bfloat16", device="cuda:0", options=options,
+                            use_cuda_graph=not (args.no_cuda_graph or args.kernel_times),
+                            kernel_options=KernelOptions.from_env())
+            loaded = engine.loaded
+            sampler = Sampler(vocab, 8, 8, engine.device)
+            timer = KernelTimer() if args.kernel_times else None
+            ms, launches, context = time_decode(loaded, sampler, 8, args.steps, args.warmup, PROMPT_TOKENS, 1, timer=timer)
+            point = {"parameters_m": round(loaded.model.weight_bytes() / 2e6, 1),
+                     "decode_b8_ms_per_step": round(ms, 4), "decode_b8_tokens_per_s": round(8e3 / ms, 1),
+                     "decode_launches_per_step": round(launches / args.steps, 1),
+                     "decode_weight_stream_frac": round(loaded.model.weight_bytes() / (ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4)}
+            if timer is not None:
+                point["decode_kernel_us_per_step"] = timer.table(args.steps)
+                timer = KernelTimer()
+                with timer:
+                    prefill_ms = time_prefill(loaded, PREFILL_TOKENS, 2, 2)
+                point["prefill_kernel_us_per_run"] = timer.table(5)
+            else:
+                prefill_ms = time_prefill(loaded, PREFILL_TOKENS, 3, 2)
+            point["prefill_2048_ms"] = round(prefill_ms, 3)
+            point["prefill_tokens_per_s"] = round(PREFILL_TOKENS * 1e3 / prefill_ms, 1)
+            entry[name] = point
+            del engine, loaded, sampler
+            torch.cuda.empty_cache()
+        record["sizes"][tag] = entry
+    return record
+
+
 def percentile(samples, q: float) -> float:
     if not samples:
         return 0.0
@@ -696,6 +775,9 @@ def main() -> int:
     parser.add_argument("--new-tokens", type=int, default=0, help="--workload: tokens to generate per request")
     parser.add_argument("--max-batched-tokens", type=int, default=0, help="--workload: token budget of a step")
     parser.add_argument("--prefill-chunk", type=int, default=0, help="--workload: longest prompt portion")
+    parser.add_argument("--design", default=None, choices=["ramosun"],
+                        help="prefill and decode of that design beside the closest LFM2 model at equal size")
+    parser.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES), help="--design: one size only")
     parser.add_argument("--no-warmup-run", action="store_true",
                         help="--workload: skip the untimed run before the timed one (for profilers)")
     args = parser.parse_args()
@@ -706,6 +788,8 @@ def main() -> int:
         args.warmup = 3
     if args.impl == "reference":
         result = run_reference(args)
+    elif args.design:
+        result = run_design(args)
     elif args.workload:
         result = run_workload(args)
     else:

@@ -9,12 +9,12 @@
 //   delta   S~ = g S;  u = beta (v - S~^T k);  S' = S~ + k u^T;  o = S'^T q
 //
 // Column j of S depends on column j alone, so a launch is cut by (span, head, run of columns) and walks the
-// span's tokens in order. A column lives in the registers of L lanes (L = 1, 2, 4 or 8 by the key size, 32
+// span's tokens in order. A column lives in the registers of L lanes (L = 1 .. 32 by the key size, 8
 // elements a lane); per token the lanes form S.k, S.q (and n.q) on the OLD state together, exchange them with
 // shuffles once, and get the read-out from them without a second pass over the new state:
 //   delta: o_j = g (S.q)_j + u_j (k.q)         mLSTM: (S'^T q)_j = a (S.q)_j + b v_j (k.q),  n'.q = a n.q + b k.q
 // Keys, queries, values and gates of the next 16 tokens are copied to shared memory (cp.async) while the
-// current 16 are worked on. A span of one token (decoding) is the same kernel: one state read, one write.
+// current 16 are worked on; the four warps of a block share them. A span of one token (decoding) is the same kernel: one state read, one write.
 //
 // Beside the scans: the gates of both mixers from their projections, the delta rule's short convolutions with
 // their carried inputs, unit norms and decay, and the per-head norm with the output gate.
@@ -22,8 +22,9 @@
 
 namespace celeg_b200 {
 
-constexpr int kScanRegs = 32;        // elements of a column a lane holds
-constexpr int kScanTile = 16;        // tokens staged at a time (8 when a column takes 8 lanes: shared memory)
+constexpr int kScanRegs = 8;         // elements of a column a lane holds
+constexpr int kScanWarps = 4;        // warps of a block: they share the staged keys and queries
+constexpr int kScanThreads = kScanWarps * 32;
 constexpr int kScanMaxDim = 256;
 
 enum ScanMode : int { kScanDelta = 0, kScanMlstm = 1 };
@@ -38,41 +39,52 @@ struct ScanParams {
     const int* span_begin; const int* span_slot;
     int heads, kv_heads, dim, vdim;
     float q_scale;
+    int vector_copies;                                   // keys and queries can be staged 16 bytes at a time
 };
 
 __device__ __forceinline__ void cp_async_4(void* smem, const void* global) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(global));
 }
+__device__ __forceinline__ void cp_async_16(void* smem, const void* global) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(global));
+}
 __device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
-// One warp a block. Element e of a column sits in lane (e / 4) % L, register 4 * (e / (4 L)) + e % 4, so that
-// the lanes of a column read consecutive 16-byte pieces of a key.
+// Four warps a block; a column of S lives in L lanes of 8 elements each (L = 1 .. 32 by the key size), so a warp
+// holds 32 / L columns and a block four times as many. Element e of a column sits in lane (e / 4) % L, register
+// 4 * (e / (4 L)) + e % 4: the lanes of a column read consecutive 16-byte pieces of a key. Few elements a lane keep
+// the chain of dependent operations per token short (the sums meet by log2 L shuffles), and many warps keep the
+// SMs busy when a step brings one long prompt.
 template <int MODE, int L>
-__global__ void __launch_bounds__(32) recurrent_scan_kernel(const ScanParams p) {
-    constexpr int kCols = 32 / L;
+__global__ void __launch_bounds__(kScanThreads) recurrent_scan_kernel(const ScanParams p) {
+    constexpr int kColsWarp = 32 / L;
+    constexpr int kCols = kScanWarps * kColsWarp;
     constexpr int kDimPad = kScanRegs * L;
-    constexpr int kTile = L == 8 ? kScanTile / 2 : kScanTile;
+    constexpr int kTile = kDimPad > 128 ? 8 : 16;       // tokens staged at a time
     __shared__ __align__(16) float k_s[2][kTile][kDimPad];
     __shared__ __align__(16) float q_s[2][kTile][kDimPad];
     __shared__ float v_s[2][kTile][kCols];
     __shared__ float g_s[2][kTile][2];
     chain_release();
-    const int lane = threadIdx.x;
-    const int sub = lane % L, col_in = lane / L;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int sub = lane % L, col_in = warp * kColsWarp + lane / L;
     const int head = blockIdx.y, span = blockIdx.z;
     const int kv_head = head / (p.heads / p.kv_heads);
     const int col = blockIdx.x * kCols + col_in;
     const bool col_ok = col < p.vdim;
     const int dim = p.dim, vdim = p.vdim;
     // keys beyond the head's size stay zero for good
-    for (int i = lane; i < 2 * kTile * kDimPad; i += 32) {
+    for (int i = tid; i < 2 * kTile * kDimPad; i += kScanThreads) {
         (&k_s[0][0][0])[i] = 0.0f;
         (&q_s[0][0][0])[i] = 0.0f;
     }
+    for (int i = tid; i < 2 * kTile * kCols; i += kScanThreads) (&v_s[0][0][0])[i] = 0.0f;
+    __syncthreads();
     chain_wait();
     const int t_begin = p.span_begin[span], t_end = p.span_begin[span + 1];
     if (t_end <= t_begin) return;
@@ -89,23 +101,32 @@ __global__ void __launch_bounds__(32) recurrent_scan_kernel(const ScanParams p) 
         if (MODE == kScanMlstm) n[r] = e < dim ? n_head[e] : 0.0f;
     }
     float m = MODE == kScanMlstm ? *m_head : 0.0f;
-    __syncwarp();
 
+    const float* k_base = p.k + (size_t)kv_head * dim;
+    const float* q_base = p.q + (size_t)(MODE == kScanMlstm ? head : kv_head) * dim;
     auto issue = [&](int t0, int stage) {
         const int count = min(kTile, t_end - t0);
-        for (int i = lane; i < count * dim; i += 32) {
-            const int tt = i / dim, e = i % dim;
-            cp_async_4(&k_s[stage][tt][e], p.k + (size_t)(t0 + tt) * p.k_stride + (size_t)kv_head * dim + e);
-            cp_async_4(&q_s[stage][tt][e], p.q + (size_t)(t0 + tt) * p.q_stride +
-                                               (size_t)(MODE == kScanMlstm ? head : kv_head) * dim + e);
+        if (p.vector_copies) {
+            const int quads = dim >> 2;
+            for (int i = tid; i < count * quads; i += kScanThreads) {
+                const int tt = i / quads, e = (i - tt * quads) << 2;
+                cp_async_16(&k_s[stage][tt][e], k_base + (size_t)(t0 + tt) * p.k_stride + e);
+                cp_async_16(&q_s[stage][tt][e], q_base + (size_t)(t0 + tt) * p.q_stride + e);
+            }
+        } else {
+            for (int i = tid; i < count * dim; i += kScanThreads) {
+                const int tt = i / dim, e = i - tt * dim;
+                cp_async_4(&k_s[stage][tt][e], k_base + (size_t)(t0 + tt) * p.k_stride + e);
+                cp_async_4(&q_s[stage][tt][e], q_base + (size_t)(t0 + tt) * p.q_stride + e);
+            }
         }
-        for (int i = lane; i < count * kCols; i += 32) {
+        for (int i = tid; i < count * kCols; i += kScanThreads) {
             const int tt = i / kCols, c = i % kCols;
             const int gc = blockIdx.x * kCols + c;
             if (gc < vdim) cp_async_4(&v_s[stage][tt][c], p.v + (size_t)(t0 + tt) * p.v_stride + (size_t)head * vdim + gc);
         }
-        for (int i = lane; i < count * 2; i += 32) {
-            const int tt = i / 2, w = i % 2;
+        for (int i = tid; i < count * 2; i += kScanThreads) {
+            const int tt = i >> 1, w = i & 1;
             cp_async_4(&g_s[stage][tt][w], p.gates + (size_t)(t0 + tt) * 2 * p.heads + w * p.heads + head);
         }
         cp_async_commit_group();
@@ -120,8 +141,9 @@ __global__ void __launch_bounds__(32) recurrent_scan_kernel(const ScanParams p) 
         } else {
             cp_async_wait<0>();
         }
-        __syncwarp();
+        __syncthreads();                                // every thread's copies of this stage have landed
         const int count = min(kTile, t_end - t0);
+#pragma unroll 2
         for (int tt = 0; tt < count; ++tt) {
             float kk[kScanRegs], qq[kScanRegs];
 #pragma unroll
@@ -131,7 +153,7 @@ __global__ void __launch_bounds__(32) recurrent_scan_kernel(const ScanParams p) 
                 kk[4 * r4] = kv4.x; kk[4 * r4 + 1] = kv4.y; kk[4 * r4 + 2] = kv4.z; kk[4 * r4 + 3] = kv4.w;
                 qq[4 * r4] = qv4.x; qq[4 * r4 + 1] = qv4.y; qq[4 * r4 + 2] = qv4.z; qq[4 * r4 + 3] = qv4.w;
             }
-            // four partial sums each, so that no chain of dependent additions is longer than a quarter
+            // sums over this lane's elements on the OLD state, in four partial sums each
             float sk[4] = {0.f, 0.f, 0.f, 0.f}, sq[4] = {0.f, 0.f, 0.f, 0.f}, kq[4] = {0.f, 0.f, 0.f, 0.f};
             float nq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -180,7 +202,7 @@ __global__ void __launch_bounds__(32) recurrent_scan_kernel(const ScanParams p) 
             }
             if (sub == 0 && col_ok) p.out[(size_t)(t0 + tt) * p.heads * vdim + (size_t)head * vdim + col] = o;
         }
-        __syncwarp();                                   // the stage is free for the tile after the next
+        __syncthreads();                                // the stage is free for the tile after the next
     }
 #pragma unroll
     for (int r = 0; r < kScanRegs; ++r) {
@@ -188,7 +210,7 @@ __global__ void __launch_bounds__(32) recurrent_scan_kernel(const ScanParams p) 
         if (col_ok && e < dim) s_head[(size_t)e * vdim + col] = s[r];
         if (MODE == kScanMlstm && blockIdx.x == 0 && col_in == 0 && e < dim) n_head[e] = n[r];
     }
-    if (MODE == kScanMlstm && blockIdx.x == 0 && lane == 0) *m_head = m;
+    if (MODE == kScanMlstm && blockIdx.x == 0 && tid == 0) *m_head = m;
 }
 
 // mLSTM: log input gate cap tanh((x_i + b_i) / cap) and log forget gate logsigmoid(cap tanh((x_f + b_f) / cap))
@@ -317,13 +339,18 @@ __global__ void gated_head_norm_kernel(const float* o, const float* gate, int ga
 
 template <int MODE>
 static int launch_scan(const ScanParams& p, int spans, cudaStream_t stream) {
-    const int lanes = p.dim <= 32 ? 1 : p.dim <= 64 ? 2 : p.dim <= 128 ? 4 : 8;
-    const int cols = 32 / lanes;
+    int lanes = 1;
+    while (lanes * kScanRegs < p.dim) lanes <<= 1;           // 1 .. 32 for key sizes up to 256
+    const int cols = kScanWarps * (32 / lanes);
     dim3 grid((p.vdim + cols - 1) / cols, p.heads, spans);
-    if (lanes == 1) launch_chained(recurrent_scan_kernel<MODE, 1>, grid, 32, 0, stream, p);
-    else if (lanes == 2) launch_chained(recurrent_scan_kernel<MODE, 2>, grid, 32, 0, stream, p);
-    else if (lanes == 4) launch_chained(recurrent_scan_kernel<MODE, 4>, grid, 32, 0, stream, p);
-    else launch_chained(recurrent_scan_kernel<MODE, 8>, grid, 32, 0, stream, p);
+    switch (lanes) {
+        case 1: launch_chained(recurrent_scan_kernel<MODE, 1>, grid, kScanThreads, 0, stream, p); break;
+        case 2: launch_chained(recurrent_scan_kernel<MODE, 2>, grid, kScanThreads, 0, stream, p); break;
+        case 4: launch_chained(recurrent_scan_kernel<MODE, 4>, grid, kScanThreads, 0, stream, p); break;
+        case 8: launch_chained(recurrent_scan_kernel<MODE, 8>, grid, kScanThreads, 0, stream, p); break;
+        case 16: launch_chained(recurrent_scan_kernel<MODE, 16>, grid, kScanThreads, 0, stream, p); break;
+        default: launch_chained(recurrent_scan_kernel<MODE, 32>, grid, kScanThreads, 0, stream, p); break;
+    }
     return check_launch("recurrent_scan");
 }
 
@@ -344,8 +371,10 @@ CELEG_API int celeg_recurrent_scan(int mode, const float* q, int q_stride, const
     CELEG_REQUIRE(mode == kScanDelta || mode == kScanMlstm, "recurrent_scan: unknown mode %d", mode);
     CELEG_REQUIRE(spans <= 65535 && heads <= 65535, "recurrent_scan: %d spans or %d heads exceed one launch", spans, heads);
     if (spans == 0) return 0;
+    const int vector_copies = dim % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 &&
+                              (((size_t)q | (size_t)k) & 15) == 0;
     const ScanParams p = {q, k, v, q_stride, k_stride, v_stride, gates, out, state, slot_stride, span_begin, span_slot,
-                          heads, kv_heads, dim, vdim, q_scale};
+                          heads, kv_heads, dim, vdim, q_scale, vector_copies};
     return mode == kScanDelta ? launch_scan<kScanDelta>(p, spans, stream) : launch_scan<kScanMlstm>(p, spans, stream);
 }
 

@@ -88,7 +88,16 @@ LOOP_ONCE = config(64, 32, [
     with_mlp(delta(2, 1, 16, 8, conv=4), 48),
 ], loop=(0, 2, 1), softcap=5.0)
 
-CONFIGS = {"mixed": (MIXED, 11), "loop_from_start": (LOOP_FROM_START, 12), "straight": (STRAIGHT, 13),
+# sizes that fit no vector width: a model width of 36, head sizes of 12 and 20, seventeen query heads on one key
+# head (more than the split-key kernel groups), key size 24 with values of 7
+ODD = config(50, 36, [
+    with_mlp(attention(3, 1, 12, 9, rot_dims=6, base=50.0), 44),
+    with_mlp(delta(3, 3, 24, 7, conv=3), 20),
+    with_mlp(attention(17, 1, 20, 30, rot_dims=20, scaling={"factor": 2.0, "low": 1.0, "high": 3.0, "original": 16}), None),
+    with_mlp(mlstm(3, 12, 20, gate_cap=6.0), 28),
+], loop=(2, 4, 2), softcap=20.0)
+
+CONFIGS = {"odd": (ODD, 15), "mixed": (MIXED, 11), "loop_from_start": (LOOP_FROM_START, 12), "straight": (STRAIGHT, 13),
            "loop_once": (LOOP_ONCE, 14)}
 
 

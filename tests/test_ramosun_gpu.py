@@ -115,7 +115,7 @@ def test_portions_of_several_sizes_down_to_two_tokens(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mixed", "loop_from_start", "straight"])
+@pytest.mark.parametrize("name", ["odd", "mixed", "loop_from_start", "straight"])
 def test_batches_of_unequal_requests_equal_each_alone(models, name, dtype):
     folder, raw, tensors = models[name]
     requests = {"p": tokens_of(raw["vocab"], 70, 3), "q": tokens_of(raw["vocab"], 23, 4),
