@@ -337,6 +337,200 @@ __global__ void gated_head_norm_kernel(const float* o, const float* gate, int ga
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Decoding: every request brings one token. One block per (request, head) does everything between the input
+// projection and the output projection: the delta rule's short convolutions over the carried inputs with SiLU,
+// unit q and k, beta and decay (or the mLSTM's two gates), the state's update and read-out with a thread per
+// column (rows of S are read and written side by side: whole lines of memory), the head's root mean square, the
+// norm's weight and the output gate. Same formulas and the same sums on the old state as the scan above.
+struct DecodeStepParams {
+    const float* proj; int stride;                 // [tokens, stride] rows of the input projection
+    int q_off, k_off, v_off, gate_off, g0_off, g1_off;
+    const float* conv_kernel; const float* carried; int taps, channels;      // delta only
+    const float* bias0; const float* bias1; float cap;   // mLSTM: gate biases and cap; delta: A_log and dt_bias
+    const float* norm_w; int norm_per_head; float eps, unit_eps;
+    float* state; long long slot_stride;
+    const int* span_slot;
+    int heads, kv_heads, dim, vdim;
+    float q_scale;
+    void* out;                                     // [tokens, heads * vdim], activation type
+};
+
+template <int MODE, typename A>
+__global__ void __launch_bounds__(256) recurrent_decode_kernel(const DecodeStepParams p) {
+    extern __shared__ float decode_smem[];          // k [dim] | q [dim] | o [vdim] | partial sums [2 * warps * 32]
+    __shared__ float scratch[33];
+    chain_release();
+    chain_wait();
+    const int head = blockIdx.x, t = blockIdx.y;
+    const int dim = p.dim, vdim = p.vdim, heads = p.heads;
+    const int kv_head = head / (heads / p.kv_heads);
+    const int qk_head = MODE == kScanMlstm ? head : kv_head;
+    float* k_s = decode_smem;
+    float* q_s = k_s + dim;
+    float* o_s = q_s + dim;
+    float* part_s = o_s + vdim;
+    const float* row = p.proj + (size_t)t * p.stride;
+    const long long slot_at = (long long)p.span_slot[t] * p.slot_stride;
+    const float* carried = MODE == kScanDelta ? p.carried + slot_at : nullptr;
+
+    // a convolved channel of the delta rule: taps - 1 carried inputs (oldest first), then the token's own
+    auto convolved = [&](int c) {
+        float sum = 0.0f;
+        for (int j = 0; j + 1 < p.taps; ++j)
+            sum = fmaf(p.conv_kernel[(size_t)c * p.taps + j], carried[(size_t)j * p.channels + c], sum);
+        sum = fmaf(p.conv_kernel[(size_t)c * p.taps + p.taps - 1], row[c], sum);
+        return sum / (1.0f + expf(-sum));
+    };
+    float k2 = 0.0f, q2 = 0.0f;
+    for (int e = threadIdx.x; e < dim; e += blockDim.x) {
+        float kv, qv;
+        if (MODE == kScanDelta) {
+            kv = convolved(p.k_off + qk_head * dim + e);
+            qv = convolved(p.q_off + qk_head * dim + e);
+        } else {
+            kv = row[p.k_off + qk_head * dim + e];
+            qv = row[p.q_off + qk_head * dim + e];
+        }
+        k_s[e] = kv;
+        q_s[e] = qv;
+        k2 += kv * kv;
+        q2 += qv * qv;
+    }
+    if (MODE == kScanDelta) {
+        k2 = block_sum(k2, scratch);
+        q2 = block_sum(q2, scratch);
+        const float k_inv = 1.0f / sqrtf(k2 + p.unit_eps), q_inv = 1.0f / sqrtf(q2 + p.unit_eps);
+        for (int e = threadIdx.x; e < dim; e += blockDim.x) {
+            k_s[e] *= k_inv;
+            q_s[e] *= q_inv;
+        }
+    }
+    __syncthreads();
+    float* slot = p.state + slot_at;
+    float* s_head = slot + (size_t)head * dim * vdim;
+    float* n_head = slot + (size_t)heads * dim * vdim + (size_t)head * dim;
+    float* m_head = slot + (size_t)heads * dim * vdim + (size_t)heads * dim + head;
+    float kq = 0.0f, nq = 0.0f;
+    for (int e = threadIdx.x; e < dim; e += blockDim.x) {
+        kq = fmaf(k_s[e], q_s[e], kq);
+        if (MODE == kScanMlstm) nq = fmaf(n_head[e], q_s[e], nq);
+    }
+    kq = block_sum(kq, scratch) * p.q_scale;
+    if (MODE == kScanMlstm) nq = block_sum(nq, scratch) * p.q_scale;
+
+    float g0, g1, keep = 0.0f, write = 0.0f, lower = 1.0f, m_new = 0.0f;
+    if (MODE == kScanDelta) {
+        g0 = 1.0f / (1.0f + expf(-row[p.g0_off + head]));                      // beta
+        const float x = row[p.g1_off + head] + p.bias1[head];
+        g1 = expf(-expf(p.bias0[head]) * (fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x)))));     // decay
+    } else {
+        g0 = p.cap * tanhf((row[p.g0_off + head] + p.bias0[head]) / p.cap);     // log input gate
+        const float z = p.cap * tanhf((row[p.g1_off + head] + p.bias1[head]) / p.cap);
+        g1 = fminf(z, 0.0f) - log1pf(expf(-fabsf(z)));                          // log forget gate
+        const float m = *m_head;
+        m_new = fmaxf(g1 + m, g0);
+        keep = expf(g1 + m - m_new);
+        write = expf(g0 - m_new);
+        lower = fmaxf(fabsf(keep * nq + write * kq), expf(-m_new)) + 1e-6f;
+    }
+    // The state: a warp takes 32 neighbouring columns and every ``split``-th row of them, so that a block's warps
+    // cover the head's columns with `split` warps each; a thread's rows stay in registers between the sums and
+    // the update (up to 32 of them; beyond that they are read again), all of its loads are in flight at once, and
+    // the partial sums of a column meet in shared memory.
+    constexpr int kKeep = 32;
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int groups = (vdim + 31) >> 5;
+    const int split = max(1, warps / groups);
+    const int groups_at_once = warps / split;
+    const bool kept = dim <= kKeep * split;
+    float squares = 0.0f;
+    for (int first_group = 0; first_group < groups; first_group += groups_at_once) {
+        const int g = first_group + warp / split, part = warp % split;
+        const int j = g * 32 + lane;
+        const bool active = warp < groups_at_once * split && g < groups && j < vdim;
+        float cells[kKeep];
+        float sk = 0.0f, sq = 0.0f;
+        if (active) {
+            if (kept) {
+#pragma unroll
+                for (int i = 0; i < kKeep; ++i) {
+                    const int e = part + i * split;
+                    cells[i] = e < dim ? s_head[(size_t)e * vdim + j] : 0.0f;
+                }
+#pragma unroll
+                for (int i = 0; i < kKeep; ++i) {
+                    const int e = part + i * split;
+                    if (e < dim) {
+                        if (MODE == kScanDelta) sk = fmaf(cells[i], k_s[e], sk);
+                        sq = fmaf(cells[i], q_s[e], sq);
+                    }
+                }
+            } else {
+                for (int e = part; e < dim; e += split) {
+                    const float se = s_head[(size_t)e * vdim + j];
+                    if (MODE == kScanDelta) sk = fmaf(se, k_s[e], sk);
+                    sq = fmaf(se, q_s[e], sq);
+                }
+            }
+        }
+        __syncthreads();                              // (the partial sums of the pass before have been read)
+        part_s[warp * 32 + lane] = sk;
+        part_s[(warps + warp) * 32 + lane] = sq;
+        __syncthreads();
+        if (active) {
+            sk = sq = 0.0f;
+            const int first = (warp / split) * split;
+            for (int w = first; w < first + split; ++w) {
+                sk += part_s[w * 32 + lane];
+                sq += part_s[(warps + w) * 32 + lane];
+            }
+            sq *= p.q_scale;
+            const float vj = MODE == kScanDelta ? convolved(p.v_off + head * vdim + j) : row[p.v_off + head * vdim + j];
+            float o, scale, add;
+            if (MODE == kScanDelta) {
+                add = g0 * (vj - g1 * sk);            // u
+                scale = g1;
+                o = g1 * sq + add * kq;
+            } else {
+                add = write * vj;
+                scale = keep;
+                o = (keep * sq + add * kq) / lower;
+            }
+            if (kept) {
+#pragma unroll
+                for (int i = 0; i < kKeep; ++i) {
+                    const int e = part + i * split;
+                    if (e < dim) s_head[(size_t)e * vdim + j] = fmaf(k_s[e], add, scale * cells[i]);
+                }
+            } else {
+                for (int e = part; e < dim; e += split) {
+                    float* cell = s_head + (size_t)e * vdim + j;
+                    *cell = fmaf(k_s[e], add, scale * *cell);
+                }
+            }
+            if (part == 0) {
+                o_s[j] = o;
+                squares += o * o;
+            }
+        }
+    }
+    if (MODE == kScanMlstm) {
+        __syncthreads();                              // every thread has read n and m
+        for (int e = threadIdx.x; e < dim; e += blockDim.x) n_head[e] = fmaf(k_s[e], write, keep * n_head[e]);
+        if (threadIdx.x == 0) *m_head = m_new;
+    }
+    squares = block_sum(squares, scratch);
+    const float inv = 1.0f / sqrtf(squares / (float)vdim + p.eps);
+    const float* w = p.norm_w + (p.norm_per_head ? (size_t)head * vdim : 0);
+    A* dst = static_cast<A*>(p.out) + ((size_t)t * heads + head) * vdim;
+    for (int j = threadIdx.x; j < vdim; j += blockDim.x) {
+        const float z = row[p.gate_off + head * vdim + j];
+        const float sig = 1.0f / (1.0f + expf(-z));
+        dst[j] = from_float<A>(o_s[j] * inv * w[j] * (MODE == kScanMlstm ? sig : z * sig));
+    }
+}
+
 template <int MODE>
 static int launch_scan(const ScanParams& p, int spans, cudaStream_t stream) {
     int lanes = 1;
@@ -433,4 +627,50 @@ CELEG_API int celeg_gated_head_norm(const float* o, const float* gate, int gate_
     else
         CELEG_REQUIRE(false, "gated_head_norm: unknown dtype code %d", act_dtype);
     return check_launch("gated_head_norm");
+}
+
+// One token per request (row i of ``proj`` is request i's token, its slot span_slot[i]): everything between the
+// two projections of a matrix-state mixer in one launch. mode 0 (delta): the convolved channels [q | k | v] are
+// the first ``channels`` columns of a row, bias0 = A_log, bias1 = dt_bias, the output gate is SiLU; the carried
+// inputs are moved on by a second launch. mode 1 (mLSTM): bias0 / bias1 = the gates' biases, the gate is a sigmoid.
+CELEG_API int celeg_recurrent_decode(int mode, const float* proj, int stride, int q_off, int k_off, int v_off,
+                                     int gate_off, int g0_off, int g1_off, const float* conv_kernel, float* carried,
+                                     int taps, int channels, const float* bias0, const float* bias1, float cap,
+                                     const float* norm_w, int norm_per_head, float eps, float unit_eps, float* state,
+                                     long long slot_stride, const int* span_begin, const int* span_slot, int tokens,
+                                     int heads, int kv_heads, int dim, int vdim, float q_scale, void* out,
+                                     int act_dtype, cudaStream_t stream) {
+    CELEG_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0,
+                  "recurrent_decode: invalid sizes tokens=%d heads=%d kv_heads=%d dim=%d vdim=%d", tokens, heads,
+                  kv_heads, dim, vdim);
+    CELEG_REQUIRE(mode == kScanDelta || mode == kScanMlstm, "recurrent_decode: unknown mode %d", mode);
+    CELEG_REQUIRE(mode == kScanMlstm || (taps >= 1 && taps <= 16 && conv_kernel && (taps == 1 || carried)),
+                  "recurrent_decode: the delta rule needs its kernel of 1 to 16 taps and the carried inputs");
+    CELEG_REQUIRE(act_dtype == kFloat32 || act_dtype == kBFloat16, "recurrent_decode: unknown dtype code %d", act_dtype);
+    CELEG_REQUIRE(tokens <= 65535, "recurrent_decode: %d tokens exceed one launch", tokens);
+    constexpr int kDecodeStepThreads = 256;
+    const size_t smem = (size_t)(2 * dim + vdim + 2 * kDecodeStepThreads) * sizeof(float);
+    CELEG_REQUIRE(smem <= 40 * 1024, "recurrent_decode: head sizes %d and %d exceed a block's shared memory", dim, vdim);
+    if (tokens == 0) return 0;
+    const DecodeStepParams p = {proj, stride, q_off, k_off, v_off, gate_off, g0_off, g1_off, conv_kernel, carried, taps,
+                                channels, bias0, bias1, cap, norm_w, norm_per_head, eps, unit_eps, state, slot_stride,
+                                span_slot, heads, kv_heads, dim, vdim, q_scale, out};
+    dim3 grid(heads, tokens);
+    if (mode == kScanDelta) {
+        if (act_dtype == kFloat32)
+            launch_chained(recurrent_decode_kernel<kScanDelta, float>, grid, kDecodeStepThreads, smem, stream, p);
+        else
+            launch_chained(recurrent_decode_kernel<kScanDelta, __nv_bfloat16>, grid, kDecodeStepThreads, smem, stream, p);
+        int status = check_launch("recurrent_decode");
+        if (status != 0 || taps == 1) return status;
+        const long long units = (long long)tokens * channels;
+        launch_chained(carried_inputs_update_kernel, (unsigned)((units + 127) / 128), 128, 0, stream, proj, stride,
+                       carried, slot_stride, span_begin, span_slot, tokens, channels, taps);
+        return check_launch("carried_inputs_update");
+    }
+    if (act_dtype == kFloat32)
+        launch_chained(recurrent_decode_kernel<kScanMlstm, float>, grid, kDecodeStepThreads, smem, stream, p);
+    else
+        launch_chained(recurrent_decode_kernel<kScanMlstm, __nv_bfloat16>, grid, kDecodeStepThreads, smem, stream, p);
+    return check_launch("recurrent_decode");
 }

@@ -94,6 +94,9 @@ _SIGNATURES = {
     "celeg_softcap": [c_void_p, c_longlong, c_float, c_void_p],
     "celeg_recurrent_scan": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                              c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "celeg_recurrent_decode": [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                               c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_float, c_float, c_void_p, c_longlong,
+                               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
     "celeg_mlstm_gates": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p],
     "celeg_delta_prepare": [c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -578,6 +581,25 @@ def recurrent_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     _check(library().celeg_recurrent_scan(mode, _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0),
                                           _ptr(gates), _ptr(out), _ptr(state), slot_stride, _ptr(span_begin),
                                           _ptr(span_slot), spans, heads, kv_heads, dim, vdim, q_scale, _stream()))
+
+
+def recurrent_decode(mode: int, proj: torch.Tensor, offsets: Tuple[int, int, int, int, int, int],
+                     conv_kernel: Optional[torch.Tensor], carried: Optional[torch.Tensor], taps: int, channels: int,
+                     bias0: torch.Tensor, bias1: torch.Tensor, cap: float, norm_weight: torch.Tensor,
+                     norm_per_head: bool, eps: float, unit_eps: float, state: torch.Tensor, slot_stride: int,
+                     span_begin: torch.Tensor, span_slot: torch.Tensor, tokens: int, heads: int, kv_heads: int,
+                     dim: int, vdim: int, q_scale: float, out: torch.Tensor) -> None:
+    """A decoding step of a matrix-state mixer between its two projections, one launch (the delta rule's carried
+    inputs: a second): row i of ``proj`` (float32) is the one token of request i. ``offsets``: columns of
+    (q, k, v, output gate, first gate, second gate) in a row. See csrc/recurrent_scan.cu."""
+    assert proj.dtype == torch.float32 and proj.stride(-1) == 1 and out.is_contiguous() and out.shape[1] == heads * vdim
+    _check(library().celeg_recurrent_decode(
+        mode, _ptr(proj), proj.stride(0), *offsets, _ptr(conv_kernel), _ptr(carried), taps, channels, _ptr(bias0),
+        _ptr(bias1), cap, _ptr(norm_weight), int(norm_per_head), eps, unit_eps, _ptr(state), slot_stride,
+        _ptr(span_begin), _ptr(span_slot), tokens, heads, kv_heads, dim, vdim, q_scale, _ptr(out),
+        dtype_code(out.dtype), _stream()))
+    global LAUNCHES
+    LAUNCHES += 1 if (mode == SCAN_DELTA and taps > 1) else 0
 
 
 def mlstm_gates(pre_i: torch.Tensor, pre_f: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float,

@@ -75,6 +75,17 @@ class MlstmMixer:
         gate = rows[:, at:at + self.v_width]; at += self.v_width
         pre_i = rows[:, at:at + self.heads]; at += self.heads
         pre_f = rows[:, at:at + self.heads]
+        if step.max_span == 1 and step.spans == t:
+            # every request brings one token: gates, state update, read-out, norm and output gate in one launch
+            width = self.qk_width
+            offsets = (0, width, 2 * width, 2 * width + self.v_width, 2 * width + 2 * self.v_width,
+                       2 * width + 2 * self.v_width + self.heads)
+            kernels.recurrent_decode(kernels.SCAN_MLSTM, rows, offsets, None, None, 0, 0, self.bias_i, self.bias_f,
+                                     self.cap, self.norm, True, self.eps, 0.0, b.state, b.slot_stride, step.span_begin,
+                                     step.span_slot, t, self.heads, self.heads, self.dim, self.vdim, self.dim ** -0.5,
+                                     self.gated)
+            rt.linear(self.gated, self.w_out, out, t)
+            return
         kernels.mlstm_gates(pre_i, pre_f, self.bias_i, self.bias_f, self.cap, self.gates, t, self.heads)
         kernels.recurrent_scan(kernels.SCAN_MLSTM, q, k, v, self.gates, self.read, b.state, b.slot_stride,
                                step.span_begin, step.span_slot, step.spans, self.heads, self.heads, self.dim,
@@ -149,6 +160,17 @@ class GatedDeltaMixer:
         gate = rows[:, at:at + self.v_width]; at += self.v_width
         pre_beta = rows[:, at:at + self.heads]; at += self.heads
         pre_a = rows[:, at:at + self.heads]
+        if step.max_span == 1 and step.spans == t:
+            # every request brings one token: convolutions, unit norms, gates, state update, read-out, norm and
+            # output gate in one launch, the carried inputs in a second
+            offsets = (0, self.qk_width, 2 * self.qk_width, self.channels, self.channels + self.v_width,
+                       self.channels + self.v_width + self.heads)
+            kernels.recurrent_decode(kernels.SCAN_DELTA, rows, offsets, self.kernel, self.carried, self.taps,
+                                     self.channels, self.a_log, self.dt_bias, 0.0, self.norm, False, self.eps,
+                                     self.UNIT_EPS, b.state, b.slot_stride, step.span_begin, step.span_slot, t,
+                                     self.heads, self.kv_heads, self.dim, self.vdim, self.dim ** -0.5, self.gated)
+            rt.linear(self.gated, self.w_out, out, t)
+            return
         kernels.delta_prepare(rows, self.kernel, self.carried, b.slot_stride, step.token_span, step.span_begin,
                               step.span_slot, self.convolved, pre_beta, pre_a, self.a_log, self.dt_bias, self.gates,
                               t, step.spans, self.channels, self.taps, self.kv_heads, self.dim, self.heads,

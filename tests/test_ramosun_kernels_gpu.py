@@ -332,3 +332,76 @@ def test_gated_head_norm(dtype, per_head, gate_kind):
     normed = normed * (weight.reshape(heads, vdim) if per_head else weight)
     want = normed.reshape(tokens, -1) * (plain.sigmoid(gate) if gate_kind == 0 else plain.silu(gate))
     close(out, want, dtype, scale=2.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,taps", [(3, 3, 24, 7, 3), (4, 2, 16, 24, 1), (2, 1, 64, 64, 4),
+                                                            (1, 1, 200, 300, 2), (2, 2, 40, 70, 5)])
+def test_decoding_kernel_of_the_delta_rule_equals_prepare_scan_and_norm(dtype, heads, kv_heads, dim, vdim, taps):
+    """One token per request: the single launch against the three steps that serve prompts (each of which is
+    tested against float64 above), on requests whose slots hold state and carried inputs."""
+    from celeg_b200 import kernels
+    torch.manual_seed(1)
+    tokens = 5
+    qk, vw = kv_heads * dim, heads * vdim
+    channels = 2 * qk + vw
+    proj = torch.randn(tokens, channels + vw + 2 * heads, device="cuda")
+    kernel = torch.randn(channels, taps, device="cuda") * 0.5
+    a_log, dt_bias = torch.randn(heads, device="cuda") - 1.0, torch.randn(heads, device="cuda")
+    norm = torch.rand(vdim, device="cuda") + 0.5
+    elements = heads * dim * vdim
+    stride = elements + (taps - 1) * channels + 4
+    state = torch.randn(tokens, stride, device="cuda") * 0.3
+    fused_state = state.clone()
+    begins = torch.arange(tokens + 1, dtype=torch.int32, device="cuda")
+    slots = torch.arange(tokens, dtype=torch.int32, device="cuda").flip(0).contiguous()
+    spans = torch.arange(tokens, dtype=torch.int32, device="cuda")
+    gates = torch.zeros(tokens, 2 * heads, device="cuda")
+    conv = torch.zeros(tokens, channels, device="cuda")
+    read = torch.zeros(tokens, vw, device="cuda")
+    want = torch.zeros(tokens, vw, dtype=dtype, device="cuda")
+    got = torch.zeros_like(want)
+    kernels.delta_prepare(proj, kernel, state[:, elements:], stride, spans, begins, slots, conv,
+                          proj[:, channels + vw:channels + vw + heads], proj[:, channels + vw + heads:], a_log, dt_bias,
+                          gates, tokens, tokens, channels, taps, kv_heads, dim, heads, 1e-6)
+    kernels.recurrent_scan(kernels.SCAN_DELTA, conv[:, :qk], conv[:, qk:2 * qk], conv[:, 2 * qk:], gates, read, state,
+                           stride, begins, slots, tokens, heads, kv_heads, dim, vdim, dim ** -0.5)
+    kernels.gated_head_norm(read, proj[:, channels:channels + vw], norm, False, want, tokens, heads, vdim, 1e-5,
+                            kernels.GATE_SILU)
+    kernels.recurrent_decode(kernels.SCAN_DELTA, proj, (0, qk, 2 * qk, channels, channels + vw, channels + vw + heads),
+                             kernel, fused_state[:, elements:], taps, channels, a_log, dt_bias, 0.0, norm, False, 1e-5,
+                             1e-6, fused_state, stride, begins, slots, tokens, heads, kv_heads, dim, vdim, dim ** -0.5, got)
+    close(got, want.to(torch.float64).cpu().numpy(), dtype)
+    close(fused_state, state.to(torch.float64).cpu().numpy(), torch.float32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,dim,vdim", [(3, 12, 20), (2, 64, 128), (1, 200, 8), (2, 40, 70), (1, 8, 300)])
+def test_decoding_kernel_of_the_mlstm_equals_gates_scan_and_norm(dtype, heads, dim, vdim):
+    from celeg_b200 import kernels
+    torch.manual_seed(2)
+    tokens = 5
+    qk, vw = heads * dim, heads * vdim
+    proj = torch.randn(tokens, 2 * qk + 2 * vw + 2 * heads, device="cuda")
+    bias_i, bias_f = torch.randn(heads, device="cuda"), torch.randn(heads, device="cuda") + 2.0
+    norm = torch.rand(vw, device="cuda") + 0.5
+    elements = heads * dim * vdim + heads * dim + heads
+    state = torch.randn(tokens, elements + 4, device="cuda") * 0.3
+    state[:, elements - heads:elements] = 0.7                     # running maxima
+    fused_state = state.clone()
+    begins = torch.arange(tokens + 1, dtype=torch.int32, device="cuda")
+    slots = torch.arange(tokens, dtype=torch.int32, device="cuda").flip(0).contiguous()
+    gates = torch.zeros(tokens, 2 * heads, device="cuda")
+    read = torch.zeros(tokens, vw, device="cuda")
+    want = torch.zeros(tokens, vw, dtype=dtype, device="cuda")
+    got = torch.zeros_like(want)
+    at = 2 * qk + 2 * vw
+    kernels.mlstm_gates(proj[:, at:at + heads], proj[:, at + heads:], bias_i, bias_f, 7.0, gates, tokens, heads)
+    kernels.recurrent_scan(kernels.SCAN_MLSTM, proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + vw], gates, read,
+                           state, elements + 4, begins, slots, tokens, heads, heads, dim, vdim, dim ** -0.5)
+    kernels.gated_head_norm(read, proj[:, 2 * qk + vw:at], norm, True, want, tokens, heads, vdim, 1e-5, kernels.GATE_SIGMOID)
+    kernels.recurrent_decode(kernels.SCAN_MLSTM, proj, (0, qk, 2 * qk, 2 * qk + vw, at, at + heads), None, None, 0, 0,
+                             bias_i, bias_f, 7.0, norm, True, 1e-5, 0.0, fused_state, elements + 4, begins, slots, tokens,
+                             heads, heads, dim, vdim, dim ** -0.5, got)
+    close(got, want.to(torch.float64).cpu().numpy(), dtype)
+    close(fused_state, state.to(torch.float64).cpu().numpy(), torch.float32)
