@@ -49,6 +49,15 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return scratch[32];
 }
 
+// Element-wise activations by code (the feed-forward parts name one): 0 the exact GELU (erf), 1 the tanh GELU, 2 SiLU.
+enum Activation : int { kGeluErf = 0, kGeluTanh = 1, kSilu = 2 };
+
+__device__ __forceinline__ float activate(float z, int kind) {
+    if (kind == kGeluErf) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
+    if (kind == kGeluTanh) return 0.5f * z * (1.0f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+    return z / (1.0f + expf(-z));
+}
+
 // Programmatic dependent launch. A kernel launched through launch_chained() may start while its
 // predecessor in the stream is still running; it must call chain_wait() before it reads anything
 // a predecessor wrote and before it writes anything a predecessor may still read (only constant

@@ -63,14 +63,6 @@ __global__ void join_stream_embedding_kernel(const float* residual, const A* del
     joined[(size_t)t * 2 * width + width + c] = from_float<A>(e);
 }
 
-enum Activation : int { kGeluErf = 0, kGeluTanh = 1, kSilu = 2 };
-
-__device__ __forceinline__ float activate(float z, int kind) {
-    if (kind == kGeluErf) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
-    if (kind == kGeluTanh) return 0.5f * z * (1.0f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
-    return z / (1.0f + expf(-z));
-}
-
 template <typename A>
 __global__ void activation_kernel(const A* in, A* out, long long count, int kind) {
     chain_release();

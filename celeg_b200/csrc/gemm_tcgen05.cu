@@ -27,13 +27,14 @@ namespace celeg_b200 {
 
 constexpr int kGemmThreads = 128;
 
-enum TcEpilogue : int { kTcStoreBf16 = 0, kTcStoreF32 = 1, kTcSwiGlu = 2 };
+enum TcEpilogue : int { kTcStoreBf16 = 0, kTcStoreF32 = 1, kTcSwiGlu = 2, kTcActivation = 3 };
 
 struct TcGemmParams {
     int m, n, k;           // n: columns of C (for SwiGLU: the inner width, B has 2n rows)
     void* c;
     int ldc;
     int* error_flag;
+    int activation;        // kTcActivation: which (common.cuh)
 };
 
 template <int BN, int STAGES, int EPI>
@@ -136,6 +137,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const float up = __bfloat162float(__float2bfloat16_rn(u[i]));
                     v[i] = g / (1.0f + expf(-g)) * up;
                 }
+            }
+            if (EPI == kTcActivation) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)        // the product as a plain product would store it, then the activation
+                    v[i] = activate(__bfloat162float(__float2bfloat16_rn(v[i])), p.activation);
             }
             if (row < p.m) {
                 const int col = n0 + c0;
@@ -328,6 +334,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                         v[i] = g / (1.0f + expf(-g)) * up;
                     }
                 }
+                if (EPI == kTcActivation) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        v[i] = activate(__bfloat162float(__float2bfloat16_rn(v[i])), p.activation);
+                }
                 if (row < p.m) {
                     const int col = n0 + c0;
                     if (EPI == kTcStoreF32) {
@@ -488,7 +499,7 @@ using namespace celeg_b200;
 
 // c[m, n] = a[m, k] * b[n, k]^T in bfloat16 with float32 accumulation on tcgen05 tensor cores.
 // epilogue 0: c bfloat16; 1: c float32; 2: b holds n gate rows then n up rows, c bfloat16 [m, n] =
-// silu(a gate^T) * (a up^T). k, lda and ldb must be multiples of 8 (16-byte rows for TMA); operands
+// silu(a gate^T) * (a up^T); 3, 4, 5: c bfloat16 = act(a b^T) with the exact GELU, the tanh GELU, SiLU. k, lda and ldb must be multiples of 8 (16-byte rows for TMA); operands
 // 16-byte aligned. error_flag (device int) receives a code if a bounded wait inside the kernel ran out.
 // forced_variant: -1 = the kernel is chosen from the shape, 0..3 = that one (for measurements).
 CELEG_API int celeg_gemm_tcgen05(const void* a, int lda, const void* b, int ldb, void* c, int ldc, int m, int n, int k,
@@ -498,7 +509,7 @@ CELEG_API int celeg_gemm_tcgen05(const void* a, int lda, const void* b, int ldb,
                   "gemm_tcgen05: k=%d, lda=%d and ldb=%d must be multiples of 8 and cover k", k, lda, ldb);
     CELEG_REQUIRE((((size_t)a | (size_t)b) & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
     CELEG_REQUIRE(ldc >= n && error_flag != nullptr, "gemm_tcgen05: ldc=%d is smaller than n=%d, or no error flag", ldc, n);
-    CELEG_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_tcgen05: unknown epilogue %d", epilogue);
+    CELEG_REQUIRE(epilogue >= 0 && epilogue <= 5, "gemm_tcgen05: unknown epilogue %d", epilogue);
     CELEG_REQUIRE((m + kTileM - 1) / kTileM <= 65535, "gemm_tcgen05: %d rows exceed one launch", m);
     // Which kernel: many rows -> the persistent kernel (128 x 256 tiles, epilogue hidden under the next
     // tile); few rows -> 128 x 128 tiles with two blocks per SM, which gives more blocks to spread the
@@ -510,13 +521,16 @@ CELEG_API int celeg_gemm_tcgen05(const void* a, int lda, const void* b, int ldb,
     if (!tensor_map_for(a, m, k, lda, kTileM, &map_a)) return -3;
     const long long b_rows = epilogue == kTcSwiGlu ? 2ll * n : n;
     if (!tensor_map_for(b, b_rows, k, ldb, epilogue == kTcSwiGlu ? bn / 2 : bn, &map_b)) return -3;
-    TcGemmParams p{m, n, k, c, ldc, error_flag};
+    TcGemmParams p{m, n, k, c, ldc, error_flag, epilogue >= kTcActivation ? epilogue - kTcActivation : 0};
+    if (epilogue > kTcActivation) epilogue = kTcActivation;
 #define CELEG_TC_DISPATCH(BN, STAGES)                                                        \
     switch (epilogue) {                                                                      \
         case kTcStoreBf16:                                                                   \
             return launch_tc<BN, STAGES, kTcStoreBf16>(map_a, map_b, p, stream);             \
         case kTcStoreF32:                                                                    \
             return launch_tc<BN, STAGES, kTcStoreF32>(map_a, map_b, p, stream);              \
+        case kTcActivation:                                                                  \
+            return launch_tc<BN, STAGES, kTcActivation>(map_a, map_b, p, stream);            \
         default:                                                                             \
             return launch_tc<BN, STAGES, kTcSwiGlu>(map_a, map_b, p, stream);                \
     }
@@ -526,6 +540,8 @@ CELEG_API int celeg_gemm_tcgen05(const void* a, int lda, const void* b, int ldb,
                 return launch_tc_persistent<kTcStoreBf16>(map_a, map_b, p, stream);
             case kTcStoreF32:
                 return launch_tc_persistent<kTcStoreF32>(map_a, map_b, p, stream);
+            case kTcActivation:
+                return launch_tc_persistent<kTcActivation>(map_a, map_b, p, stream);
             default:
                 return launch_tc_persistent<kTcSwiGlu>(map_a, map_b, p, stream);
         }

@@ -32,7 +32,8 @@ namespace celeg_b200 {
 
 constexpr int kGemvMaxConvTaps = 16;
 
-enum GemvMode : int { kGemvStoreBf16 = 0, kGemvStoreF32 = 1, kGemvAddResidual = 2, kGemvSwiGlu = 3, kGemvConv = 4 };
+enum GemvMode : int { kGemvStoreBf16 = 0, kGemvStoreF32 = 1, kGemvAddResidual = 2, kGemvSwiGlu = 3, kGemvConv = 4,
+                      kGemvActivation = 5 };     // y bfloat16 = act(x w^T); which activation travels in the `taps` argument
 
 struct GemvConvArgs {
     const float* conv_w;         // [channels, taps]
@@ -304,6 +305,10 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
         }
         if (MODE == kGemvStoreBf16) {
             reinterpret_cast<__nv_bfloat16*>(y)[(size_t)out_row * ldy + out_col] = __float2bfloat16_rn(sum[0]);
+        } else if (MODE == kGemvActivation) {
+            // the product as a plain product would store it (one rounding), then the activation
+            const float z = __bfloat162float(__float2bfloat16_rn(sum[0]));
+            reinterpret_cast<__nv_bfloat16*>(y)[(size_t)out_row * ldy + out_col] = __float2bfloat16_rn(activate(z, conv.taps));
         } else if (MODE == kGemvStoreF32) {
             reinterpret_cast<float*>(y)[(size_t)out_row * ldy + out_col] = sum[0];
         } else if (MODE == kGemvAddResidual) {
@@ -402,6 +407,8 @@ static int launch_gemv(int mode, const __nv_bfloat16* x, int ldx, const __nv_bfl
             return launch_one<MT, 1, kGemvStoreBf16, UNROLL, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, 0, conv, norm, stream);
         case kGemvStoreF32:
             return launch_one<MT, 1, kGemvStoreF32, UNROLL, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, 0, conv, norm, stream);
+        case kGemvActivation:
+            return launch_one<MT, 1, kGemvActivation, UNROLL, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, 0, conv, norm, stream);
         case kGemvAddResidual:
             return launch_one<MT, 1, kGemvAddResidual, UNROLL, WARPS>(x, ldx, w, ldw, y, ldy, m, n, k, 0, conv, norm, stream);
         case kGemvSwiGlu:

@@ -369,8 +369,9 @@ def attention_prefill_tcgen05(q: torch.Tensor, q_row_stride: int, out: torch.Ten
         head_dim, page_tokens, int(window or 0), scale, _ptr(error_flag), _stream()))
 
 
+ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU = 0, 1, 2      # codes of csrc/common.cuh: activate()
 GEMV_MAX_ROWS = 16
-GEMV_STORE, GEMV_STORE_F32, GEMV_ADD_RESIDUAL, GEMV_SWIGLU, GEMV_CONV = 0, 1, 2, 3, 4
+GEMV_STORE, GEMV_STORE_F32, GEMV_ADD_RESIDUAL, GEMV_SWIGLU, GEMV_CONV, GEMV_ACTIVATION = 0, 1, 2, 3, 4, 5
 
 
 def gemv_supported(rows: int, x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -388,7 +389,9 @@ def gemv_bf16(x, w: torch.Tensor, y: torch.Tensor, rows: int, mode: int = GEMV_S
     [2*inner, k] (gate rows, then up rows) and y bfloat16 [rows, inner] = silu(gate) * up; GEMV_CONV: w is
     [3*channels, k] (B, C, X rows of the short convolution's input projection), y bfloat16
     [rows, channels] = C * conv(B*X) over each request's carried state, which is shifted; row i is the
-    single token of request i, whose state slot is span_slot[i].
+    single token of request i, whose state slot is span_slot[i]. GEMV_ACTIVATION: y bfloat16 = act(x w^T) with
+    ``taps`` = ACT_GELU_ERF, ACT_GELU_TANH or ACT_SILU (the product rounded to bfloat16 first, as a plain product
+    stores it).
     ``x`` may be a :class:`SplitNorm` (the operand still lacks its row scale; applied to the sums here).
     With ``prepare`` (GEMV_ADD_RESIDUAL only): the first half of the norm that follows, weight
     ``next_weight``, is written too: ``prepare.xw`` and this product's pieces of the sums of squares.
@@ -427,6 +430,7 @@ def gemv_bf16(x, w: torch.Tensor, y: torch.Tensor, rows: int, mode: int = GEMV_S
 
 
 TC_STORE, TC_STORE_F32, TC_SWIGLU = 0, 1, 2
+TC_ACTIVATION = 3          # + ACT_GELU_ERF, ACT_GELU_TANH or ACT_SILU: y bfloat16 = act(x w^T)
 
 
 def gemm_tcgen05_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -548,9 +552,6 @@ def join_stream_embedding(residual: torch.Tensor, delta_a: Optional[torch.Tensor
     _check(library().celeg_join_stream_embedding(_ptr(residual), _ptr(delta_a), _ptr(delta_b), _ptr(table), _ptr(tokens),
                                                  _ptr(joined), n_rows, width, table.shape[0], multiplier,
                                                  dtype_code(joined.dtype), _stream()))
-
-
-ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU = 0, 1, 2
 
 
 def activation(x: torch.Tensor, out: torch.Tensor, rows: int, kind: int) -> None:

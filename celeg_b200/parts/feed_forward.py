@@ -64,6 +64,5 @@ class DenseFeedForward:
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
         rt, t = self.rt, step.tokens
-        rt.linear(x, self.w_up, self.raised, t)
-        kernels.activation(self.raised, self.raised, t, self.activation)
+        rt.linear_activation(x, self.w_up, self.raised, t, self.activation)
         rt.linear(self.raised, self.w_down, out, t)

@@ -296,6 +296,26 @@ class Runtime:
         self.linear(x, gate_up_weight, scratch, rows)
         kernels.swiglu(scratch, out, rows, inner)
 
+    def linear_activation(self, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int, kind: int) -> None:
+        """out[:rows] = act(x[:rows] @ weight.T), ``kind`` one of kernels.ACT_*. Few bfloat16 rows: the
+        weight-streaming kernel with the activation in its epilogue; very many: the tcgen05 kernel with it (where
+        the gate|up product of a SwiGLU goes there too); otherwise the product and the activation kernel."""
+        if rows == 0:
+            return
+        operand = x.xw if isinstance(x, kernels.SplitNorm) else x
+        if self.act_dtype == torch.bfloat16 and kernels.gemv_supported(rows, operand, weight):
+            kernels.gemv_bf16(x, weight, out, rows, kernels.GEMV_ACTIVATION, taps=kind, ahead=self._ahead(weight))
+            return
+        if (self.act_dtype == torch.bfloat16 and kernels.gemm_tcgen05_supported(x, weight)
+                and (self.tensor_core_products == "all"
+                     or (self.tensor_core_products == "swiglu" and rows >= self.tensor_core_min_rows
+                         and weight.shape[1] >= self.tensor_core_min_width))):
+            kernels.gemm_tcgen05(x, weight, out, rows, kernels.TC_ACTIVATION + kind, self.error_flag,
+                                 self.tensor_core_variant)
+            return
+        self.linear(x, weight, out, rows)
+        kernels.activation(out, out, rows, kind)
+
     def linear_short_conv(self, x: torch.Tensor, in_weight: torch.Tensor, conv_kernel: torch.Tensor, taps: int,
                           binding, out: torch.Tensor, step: "StepContext") -> bool:
         """The short convolution's input projection with its gate fused in, for steps in which every

@@ -405,3 +405,30 @@ def test_decoding_kernel_of_the_mlstm_equals_gates_scan_and_norm(dtype, heads, d
                              heads, heads, dim, vdim, dim ** -0.5, got)
     close(got, want.to(torch.float64).cpu().numpy(), dtype)
     close(fused_state, state.to(torch.float64).cpu().numpy(), torch.float32)
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2])
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (8, 1000, 256), (16, 48, 520), (5, 70, 136)])
+def test_small_batch_product_with_an_activation_in_its_epilogue(m, n, k, kind):
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(9)
+    x, w = rounded(rng.normal(size=(m, k)), torch.bfloat16), rounded(rng.normal(size=(n, k)) * 0.2, torch.bfloat16)
+    y = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    kernels.gemv_bf16(dev(x, torch.bfloat16), dev(w, torch.bfloat16), y, m, kernels.GEMV_ACTIVATION, taps=kind)
+    product = rounded(x @ w.T, torch.bfloat16)
+    want = [plain.gelu_erf, lambda z: 0.5 * z * (1 + np.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3))), plain.silu][kind](product)
+    close(y, want, torch.bfloat16, scale=2.0)
+
+
+@pytest.mark.parametrize("variant", [1, 3, -1])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 264, 520), (2048, 384, 1024)])
+def test_tcgen05_product_with_an_activation_in_its_epilogue(m, n, k, variant):
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(10)
+    x, w = rounded(rng.normal(size=(m, k)), torch.bfloat16), rounded(rng.normal(size=(n, k)) * 0.1, torch.bfloat16)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    kernels.gemm_tcgen05(dev(x, torch.bfloat16), dev(w, torch.bfloat16), y, m, kernels.TC_ACTIVATION + kernels.ACT_GELU_ERF,
+                         flag, variant)
+    assert int(flag.item()) == 0
+    close(y, plain.gelu_erf(rounded(x @ w.T, torch.bfloat16)), torch.bfloat16, scale=2.0)
