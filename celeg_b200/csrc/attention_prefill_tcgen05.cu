@@ -55,6 +55,7 @@ struct FaParams {
     int table_stride;
     int spans, q_heads, kv_heads, page_tokens, window;
     float scale_log2;              // softmax scale * log2(e)
+    const float* sinks;            // [q_heads] or null: a score per head in every row's denominator, no key, no value
     int* error_flag;
 };
 
@@ -361,7 +362,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             if (!ok) {
                 if (lane == 0) atomicExch(p.error_flag, 65);
             } else if (live) {
-                const float inv = run_sum > 0.0f ? 1.0f / run_sum : 0.0f;
+                // a sink joins the denominator relative to the maximum the sum is relative to (a row without a
+                // key in reach has none and no output either)
+                const float sink_part = (p.sinks && run_sum > 0.0f)
+                                            ? exp2f(p.sinks[h] * 1.4426950408889634f - used_max) : 0.0f;
+                const float inv = run_sum > 0.0f ? 1.0f / (run_sum + sink_part) : 0.0f;
                 __nv_bfloat16* dst = p.out + ((size_t)(t0 + row) * p.q_heads + h) * kFaD;
 #pragma unroll
                 for (int c0 = 0; c0 < kFaD; c0 += 8) {
@@ -398,8 +403,8 @@ CELEG_API int celeg_attention_prefill_tcgen05(const void* q, int q_row_stride, i
                                               const void* v_cache, int pages, const int* positions,
                                               const int* span_begin, const int* block_table, int table_stride,
                                               int tokens, int spans, int tile_count, int q_heads, int kv_heads,
-                                              int head_dim, int page_tokens, int window, float scale, int* error_flag,
-                                              cudaStream_t stream) {
+                                              int head_dim, int page_tokens, int window, float scale,
+                                              const float* sinks, int* error_flag, cudaStream_t stream) {
     CELEG_REQUIRE(celeg_attention_prefill_tcgen05_supported(q_heads, kv_heads, head_dim, page_tokens),
                   "attention_prefill_tcgen05: head_dim=%d page_tokens=%d q_heads=%d kv_heads=%d are not taken here",
                   head_dim, page_tokens, q_heads, kv_heads);
@@ -426,6 +431,7 @@ CELEG_API int celeg_attention_prefill_tcgen05(const void* q, int q_row_stride, i
     p.page_tokens = page_tokens;
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.sinks = sinks;
     p.error_flag = error_flag;
     const cudaError_t status = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel,
                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFaSmemBytes);

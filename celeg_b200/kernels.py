@@ -61,7 +61,7 @@ _SIGNATURES = {
                                 c_void_p, c_void_p, c_void_p],
     "celeg_attention_prefill_tcgen05": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                        c_float, c_void_p, c_void_p],
+                                        c_float, c_void_p, c_void_p, c_void_p],
     "celeg_gemv_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                         c_void_p, c_longlong, c_void_p, c_void_p],
     "celeg_gemv_prefetch_next": [c_void_p, c_longlong],
@@ -358,15 +358,17 @@ def attention_prefill_tcgen05(q: torch.Tensor, q_row_stride: int, out: torch.Ten
                               v_cache: torch.Tensor, positions: torch.Tensor, span_begin: torch.Tensor,
                               block_table: torch.Tensor, tokens: int, spans: int, tile_count: int, q_heads: int,
                               kv_heads: int, head_dim: int, page_tokens: int, window: Optional[int], scale: float,
-                              error_flag: torch.Tensor) -> None:
+                              error_flag: torch.Tensor, sinks: Optional[torch.Tensor] = None) -> None:
     """Prompt-portion attention on tcgen05 (S and O' in tensor memory, Q/K/V by TMA).
     ``tile_count`` = sum over the spans of ceil(length / 128)."""
     if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
         raise KernelLibraryError("attention_prefill_tcgen05 needs contiguous cache layers")
+    if sinks is not None:
+        _need(sinks, torch.float32, "sinks")
     _check(library().celeg_attention_prefill_tcgen05(
         _ptr(q), q_row_stride, q.shape[0], _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(positions),
         _ptr(span_begin), _ptr(block_table), block_table.stride(0), tokens, spans, tile_count, q_heads, kv_heads,
-        head_dim, page_tokens, int(window or 0), scale, _ptr(error_flag), _stream()))
+        head_dim, page_tokens, int(window or 0), scale, _ptr(sinks), _ptr(error_flag), _stream()))
 
 
 ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU = 0, 1, 2      # codes of csrc/common.cuh: activate()

@@ -284,15 +284,14 @@ class AttentionMixer:
         span_begin = step.span_begin[skip:]
         span_table = table[skip:]
         lengths = step.host_span_lengths[skip:] if step.host_span_lengths is not None else None
-        if (lengths is not None and rt.tcgen05_attention and self.sinks is None
-                and kernels.attention_prefill_tcgen05_supported(
+        if (lengths is not None and rt.tcgen05_attention and kernels.attention_prefill_tcgen05_supported(
                 self.heads, self.kv_heads, self.head_dim, b.page_tokens, rt.act_dtype)):
             # head size 64: S and O' in tensor memory, Q/K/V by TMA
             tiles = step.prompt_tile_bound or sum((length + 127) // 128 for length in lengths)
             kernels.attention_prefill_tcgen05(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,
                                               span_begin, span_table, step.tokens, spans, tiles, self.heads,
                                               self.kv_heads, self.head_dim, b.page_tokens, self.window, self.scale,
-                                              step.error_flag)
+                                              step.error_flag, sinks=self.sinks)
             return
         if kernels.attention_prefill_supported(self.heads, self.kv_heads, self.head_dim, rt.act_dtype):
             kernels.attention_prefill(self.qkv, self.qkv_width, self.attended, b.k, b.v, step.positions,

@@ -89,10 +89,10 @@ def sink_reference(q, k, v, pos, scale, window, sinks):
 
 
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page_tokens,window", [
-    (4, 2, 16, 16, None), (6, 6, 96, 16, 96), (6, 3, 80, 16, 37), (3, 1, 64, 8, 9), (4, 1, 40, 16, 130)])
+    (4, 2, 16, 16, None), (6, 6, 96, 16, 96), (6, 3, 80, 16, 37), (3, 1, 64, 8, 9), (4, 1, 40, 16, 130), (8, 2, 64, 16, 200), (4, 4, 64, 32, None)])
 def test_sinks_in_the_attention_kernels(heads, kv_heads, head_dim, page_tokens, window):
-    """The general kernel (both types), the tensor-core kernel for portions and the split-key kernel for single
-    tokens (several splits, and one warp an item) with a sink per head: large, small, and in between."""
+    """The general kernel (both types), the tensor-core kernels for portions (mma.sync; tcgen05 at head size 64) and
+    the split-key kernel for single tokens (several splits) with a sink per head: large, small, and in between."""
     from celeg_b200 import kernels
     rng = np.random.default_rng(3)
     sinks = np.linspace(-6.0, 5.0, heads).astype(np.float32)
@@ -124,6 +124,14 @@ def test_sinks_in_the_attention_kernels(heads, kv_heads, head_dim, page_tokens, 
                                       dev(np.array(begins, dtype=np.int32)), dev(table), tokens, len(lengths), heads,
                                       kv_heads, head_dim, page_tokens, window, scale, flag, sinks=dev(sinks))
             close(out, want, dtype, scale=1.5)
+            if kernels.attention_prefill_tcgen05_supported(heads, kv_heads, head_dim, page_tokens, dtype):
+                out = torch.zeros_like(out)
+                tiles = sum((m + 127) // 128 for m in span_len)
+                kernels.attention_prefill_tcgen05(dev(q.reshape(tokens, -1), dtype), heads * head_dim, out, k_cache, v_cache,
+                                                  args[0], dev(np.array(begins, dtype=np.int32)), dev(table), tokens,
+                                                  len(lengths), tiles, heads, kv_heads, head_dim, page_tokens, window,
+                                                  scale, flag, sinks=dev(sinks))
+                close(out, want, dtype, scale=1.5)
             # single tokens: the last token of every request, keys in chunks of 64 (up to six splits)
             last = [b - 1 for b in begins[1:]]
             single_q = dev(q[last].reshape(len(last), -1), dtype)
