@@ -194,7 +194,7 @@ class KernelTimer:
              "attention_decode_fused", "attention_prefill", "attention_prefill_tcgen05", "gemv_bf16", "gemm_tcgen05",
              "gemm_stream", "gemm_f32", "swiglu", "sample", "sample_greedy", "mark_seen",
              "add_dyt", "add_to_residual", "join_stream_embedding", "activation", "softcap", "recurrent_scan",
-             "mlstm_gates", "delta_prepare", "gated_head_norm", "qk_whole_norm_rope_store")
+             "mlstm_gates", "delta_prepare", "gated_head_norm", "qk_whole_norm_rope_store", "recurrent_decode")
 
     def __init__(self):
         self.pairs = []
