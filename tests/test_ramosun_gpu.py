@@ -335,3 +335,69 @@ def test_greedy_generation_in_bfloat16_with_graphs(models):
             if top[1] - top[0] > 0.05 * (logits.max() - logits.min()):
                 assert int(token) == int(np.argmax(logits))
             sequence.append(int(token))
+
+
+# ------------------------------------------------------------------------------- configurations drawn at random
+def random_config(rng):
+    """A configuration with every open size drawn anew: widths that are multiples of 4 only, head sizes from 4 to
+    256, groupings up to 20 query heads a key head, windows from 1 token to longer than any sequence, 1 to 6 taps,
+    the repeated run anywhere (or nowhere), layers with and without a feed-forward."""
+    width = int(rng.choice([20, 36, 64, 100, 128, 192]))
+    vocab = int(rng.integers(17, 300))
+    layers = []
+    for _ in range(int(rng.integers(1, 6))):
+        kind = rng.choice(["attention", "mlstm", "delta"])
+        if kind == "attention":
+            dim = int(rng.choice([4, 8, 12, 16, 24, 32, 64, 96, 128, 256]))
+            kv_heads = int(rng.integers(1, 4))
+            heads = kv_heads * int(rng.choice([1, 1, 2, 3, 4, 20]))
+            if heads * dim > 2048:
+                heads = kv_heads
+            window = None if rng.random() < 0.2 else int(rng.choice([1, 2, 7, 16, 17, 31, 64, 200]))
+            rot = None if rng.random() < 0.2 else int(rng.choice([d for d in (2, 4, dim // 2, dim) if d % 2 == 0 and 0 < d <= dim]))
+            scaling = None if rng.random() < 0.5 else {"factor": float(rng.choice([2.0, 8.0])), "low": 1.0,
+                                                       "high": float(rng.choice([2.0, 4.0])), "original": int(rng.choice([16, 64, 512]))}
+            layer = rm.attention(heads, kv_heads, dim, window, rot_dims=rot, base=float(rng.choice([50.0, 10000.0])),
+                                 scaling=scaling, scale=float(rng.choice([dim ** -0.5, 0.2, 1.0])))
+        elif kind == "mlstm":
+            layer = rm.mlstm(int(rng.integers(1, 4)), int(rng.choice([4, 8, 20, 32, 64, 130])), int(rng.choice([4, 9, 32, 80])),
+                             gate_cap=float(rng.choice([3.0, 15.0, 30.0])))
+        else:
+            kv_heads = int(rng.integers(1, 3))
+            layer = rm.delta(kv_heads * int(rng.choice([1, 2, 3])), kv_heads, int(rng.choice([4, 8, 20, 32, 64, 130])),
+                             int(rng.choice([4, 9, 32, 80])), conv=int(rng.integers(1, 7)))
+        layers.append(rm.with_mlp(layer, None if rng.random() < 0.3 else int(rng.choice([8, 44, 128]))))
+    loop = None
+    if rng.random() < 0.7:
+        start = int(rng.integers(0, len(layers)))
+        loop = (start, int(rng.integers(start + 1, len(layers) + 1)), int(rng.integers(1, 4)))
+    return rm.config(vocab, width, layers, loop=loop, eps=float(rng.choice([1e-5, 1e-6, 1e-3])),
+                     softcap=None if rng.random() < 0.3 else float(rng.choice([5.0, 30.0])))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(tmp_path, seed):
+    """Whole prompt, portions beside single tokens of a second request, and decoding, in both precisions."""
+    rng = np.random.default_rng(1000 + seed)
+    raw = random_config(rng)
+    folder = str(tmp_path / "drawn")
+    raw, bf16 = rm.write_model(folder, raw, 500 + seed)
+    tensors = plain.as_float64(bf16)
+    first, second = tokens_of(raw["vocab"], 75, seed), tokens_of(raw["vocab"], 33, 100 + seed)
+    want = {"a": plain.forward(raw, tensors, first), "b": plain.forward(raw, tensors, second)}
+    steps = [[("a", first[:19])], [("a", first[19:21]), ("b", second[:1])], [("b", second[1:2]), ("a", first[21:60])],
+             [("a", first[60:61]), ("b", second[2:30])]]
+    steps += [[("a", first[61 + i:62 + i])] + ([("b", second[30 + i:31 + i])] if 30 + i < len(second) else []) for i in range(14)]
+    for dtype in ("float32", "bfloat16"):
+        loaded = load(folder, dtype, page_tokens=int(rng.choice([8, 16, 32])))
+        whole = run_steps(loaded, [[("w", first)]])["w"]
+        loaded.step.end("w")
+        got = run_steps(loaded, steps)
+        if dtype == "float32":
+            check(whole, want["a"], dtype, f"{raw['layers']} whole")
+            for key in ("a", "b"):
+                check(got[key], want[key], dtype, f"{raw['layers']} request {key}")
+        else:
+            # (random sizes amplify bfloat16 rounding at will: the path must follow the plain model in the middle)
+            for rows, target in ((whole, want["a"]), (got["a"], want["a"]), (got["b"], want["b"])):
+                assert np.median(spread_error(np.asarray(rows, dtype=np.float64), target)) < 0.15
