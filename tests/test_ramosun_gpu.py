@@ -401,3 +401,75 @@ def test_configurations_drawn_at_random(tmp_path, seed):
             # (random sizes amplify bfloat16 rounding at will: the path must follow the plain model in the middle)
             for rows, target in ((whole, want["a"]), (got["a"], want["a"]), (got["b"], want["b"])):
                 assert np.median(spread_error(np.asarray(rows, dtype=np.float64), target)) < 0.15
+
+
+# ------------------------------------------------------------------------------ command line, scheduler under load
+def plain_greedy(raw, tensors, prompt, new):
+    sequence = list(prompt)
+    for _ in range(new):
+        sequence.append(int(np.argmax(plain.forward(raw, tensors, sequence)[-1])))
+    return sequence[len(prompt):]
+
+
+def test_command_line_generates_and_dumps_logits(models, tmp_path, capsys):
+    from celeg_b200.cli import main
+    folder, raw, tensors = models["straight"]
+    prompt = tokens_of(raw["vocab"], 12, 90)
+    dump = str(tmp_path / "last.f32")
+    code = main(["--model", folder, "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "6", "--dtype", "fp32",
+                 "--temperature", "0", "--repetition-penalty", "1.0", "--runtime-tokens", "--dump-logits", dump,
+                 "--context", "128"])
+    assert code == 0
+    captured = capsys.readouterr()
+    want = plain_greedy(raw, tensors, prompt, 6)
+    assert f"CELEG_GENERATED_TOKEN_IDS=[{','.join(map(str, want))}]" in captured.out
+    logits = np.fromfile(dump, dtype="<f4").astype(np.float64)
+    assert spread_error(logits[None, :], plain.forward(raw, tensors, prompt)[-1:])[0] < 2e-4
+    assert main(["--model", folder, "--print-config"]) == 0
+    assert '"architecture": "Ramosun"' in capsys.readouterr().out
+
+
+def test_many_requests_through_a_small_pool_with_preemption(models):
+    """Sixteen requests through three slots and a pool of pages that holds about two of them, growing while they
+    decode (MAX_UTILIZATION): requests wait, are left out of steps, are preempted and run again from their prompt,
+    in slots and pages others have used. Every request still gets the tokens it gets alone, wherever the plain
+    model's choice is not a near tie (float32, greedy)."""
+    from celeg_b200 import Engine, EngineOptions, RequestOptions, SamplingParams, SchedulerPolicy
+    folder, raw, tensors = models["mixed"]
+    rng = np.random.default_rng(60)
+    lengths = rng.integers(1, 50, size=16).tolist()
+    prompts = [tokens_of(raw["vocab"], n, 200 + i) for i, n in enumerate(lengths)]
+    new_tokens = rng.integers(1, 16, size=16).tolist()
+    options = EngineOptions(max_active_requests=3, max_batched_tokens=32, prefill_chunk_tokens=13, page_tokens=16,
+                            logical_kv_pages=7, scheduler_policy=SchedulerPolicy.MAX_UTILIZATION)
+    engine = Engine(folder, max_context=128, dtype="float32", options=options)
+    greedy = SamplingParams(temperature=0.0, top_k=1, repetition_penalty=1.0)
+    ids = [engine.submit(p, RequestOptions(max_new_tokens=n, eos_tokens=(), generation=greedy))
+           for p, n in zip(prompts, new_tokens)]
+    outputs = {i: [] for i in ids}
+    pending = set(ids)
+    steps = 0
+    while pending:
+        assert engine.step() or not engine.scheduler.has_work()
+        engine.loaded.manager.check_invariants()
+        for i in list(pending):
+            result = engine.poll(i)
+            outputs[i].extend(result.tokens)
+            if result.finished:
+                assert result.status.value == "finished", result.error
+                pending.discard(i)
+        steps += 1
+        assert steps < 3000
+    compared = 0
+    for i, prompt, count in zip(ids, prompts, new_tokens):
+        assert len(outputs[i]) == count
+        sequence = list(prompt)
+        for token in outputs[i]:
+            logits = plain.forward(raw, tensors, sequence)[-1]
+            top = np.sort(logits)[-2:]
+            if top[1] - top[0] > 1e-2 * (logits.max() - logits.min()):
+                assert int(token) == int(np.argmax(logits)), f"request {i} after {len(sequence)} tokens"
+                compared += 1
+            sequence.append(int(token))
+    assert compared > sum(new_tokens) // 2
+    assert engine.loaded.manager.free_slots == 3
