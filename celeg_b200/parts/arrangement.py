@@ -15,6 +15,8 @@ from __future__ import annotations
 
 from typing import Mapping
 
+import torch
+
 from .registry import register_part
 from .runtime import ResidualStream, Runtime, StepContext
 
@@ -83,7 +85,23 @@ class ParallelResidual:
             stream.add_later(self.delta_a)
             return
         x_mixer, x_ffn = stream.normed_pair(self.mixer_norm, self.normed_a, self.ffn_norm, self.normed_b, step.tokens)
-        self.mixer.forward(x_mixer, self.delta_a, step)
-        self.ffn.forward(x_ffn, self.delta_b, step)
+        rt = self.rt
+        if rt.side_by_side_branches and rt.small_batch(step.tokens):
+            # few rows: both chains are short kernels that leave most of the GPU idle, and they share nothing but
+            # their input's source. The feed-forward goes to a second stream (two branches of the step's graph
+            # when it is captured) and is joined before anything reads the stream again.
+            main, side = torch.cuda.current_stream(rt.device), rt.side_stream()
+            fork = torch.cuda.Event()
+            fork.record(main)
+            side.wait_event(fork)
+            with torch.cuda.stream(side):
+                self.ffn.forward(x_ffn, self.delta_b, step)
+                join = torch.cuda.Event()
+                join.record(side)
+            self.mixer.forward(x_mixer, self.delta_a, step)
+            main.wait_event(join)
+        else:
+            self.mixer.forward(x_mixer, self.delta_a, step)
+            self.ffn.forward(x_ffn, self.delta_b, step)
         stream.add_later(self.delta_a)
         stream.add_later_beside(self.delta_b)

@@ -40,6 +40,10 @@ class KernelOptions:
     prefetch_mb: float = 8.0
     # decode steps of at most 16 rows run the fused small-batch products (False: the general path)
     fuse_small_batches: bool = True
+    # blocks whose mixer and feed-forward read the same stream (``parallel_residual``): in steps of few rows the
+    # feed-forward runs on a second stream beside the mixer (inside the step's graph: two branches), since neither
+    # chain of short kernels fills the GPU alone
+    side_by_side_branches: bool = True
 
     def validate(self) -> None:
         if self.tensor_core_products not in ("none", "swiglu", "all"):

@@ -156,6 +156,8 @@ class Runtime:
         self.split_norms = options.split_norms
         self.fuse_decode_qk = options.fuse_decode_qk
         self.tcgen05_attention = options.tcgen05_attention
+        self.side_by_side_branches = options.side_by_side_branches
+        self._side_stream: Optional[torch.cuda.Stream] = None
         # Decode steps are a chain of short weight-streaming kernels, the same chain every step. Each of them
         # asks the first megabytes of its successor's weights into the L2, so that memory works across the
         # kernel boundary; the successor of a weight is learnt from the order of the calls (the first step of
@@ -171,6 +173,12 @@ class Runtime:
         self._scratch: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
         self.weight_bytes = 0                   # what matrix() and vector() have put on the device
         kernels.library()                       # fail now, not at the first step, if it is missing
+
+    def side_stream(self) -> torch.cuda.Stream:
+        """A second stream of this runtime's device, for work that may run beside the step's main chain."""
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(device=self.device)
+        return self._side_stream
 
     def scratch(self, tag: str, columns: int, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """A persistent [max_tokens, columns] buffer. Parts that ask with the same tag, width and
