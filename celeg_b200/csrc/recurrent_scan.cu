@@ -259,6 +259,22 @@ __global__ void delta_prepare_kernel(const DeltaPrepareArgs a) {
         // four channels a thread, 16 bytes a load: all taps' loads of a thread are in flight together
         for (int c = 4 * threadIdx.x; c < a.channels; c += 4 * blockDim.x) {
             float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (a.taps == 4) {
+                // four taps: a channel's kernel is one 16-byte load, and all eight loads are in flight together
+                float4 x[4], w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int s = rel - 3 + j;
+                    x[j] = *reinterpret_cast<const float4*>(s >= 0 ? a.proj + (size_t)(begin + s) * a.stride + c
+                                                                   : carried + (size_t)(3 + s) * a.channels + c);
+                    w[j] = __ldg(reinterpret_cast<const float4*>(a.kernel + (size_t)(c + j) * 4));
+                }
+                // (the same order of additions as the general loop: tap 0 first)
+                sum.x = fmaf(w[0].w, x[3].x, fmaf(w[0].z, x[2].x, fmaf(w[0].y, x[1].x, w[0].x * x[0].x)));
+                sum.y = fmaf(w[1].w, x[3].y, fmaf(w[1].z, x[2].y, fmaf(w[1].y, x[1].y, w[1].x * x[0].y)));
+                sum.z = fmaf(w[2].w, x[3].z, fmaf(w[2].z, x[2].z, fmaf(w[2].y, x[1].z, w[2].x * x[0].z)));
+                sum.w = fmaf(w[3].w, x[3].w, fmaf(w[3].z, x[2].w, fmaf(w[3].y, x[1].w, w[3].x * x[0].w)));
+            } else
             for (int j = 0; j < a.taps; ++j) {
                 const int s = rel - (a.taps - 1) + j;
                 const float4 x = *reinterpret_cast<const float4*>(
