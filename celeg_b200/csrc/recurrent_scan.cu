@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(kScanThreads) recurrent_scan_kernel(const Scan
         }
         __syncthreads();                                // every thread's copies of this stage have landed
         const int count = min(kTile, t_end - t0);
-#pragma unroll 2
+#pragma unroll 4
         for (int tt = 0; tt < count; ++tt) {
             float kk[kScanRegs], qq[kScanRegs];
 #pragma unroll
