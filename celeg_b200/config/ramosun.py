@@ -1,8 +1,9 @@
 """Typed configuration of the Ramosun design, read from config.json (``"architecture": "Ramosun"``).
 
 Keys: ``vocab``, ``width``, ``norm.eps``, ``logit_softcap`` (absent or null: none), ``layers`` (a list; each entry
-has ``type`` = attention | mlstm | delta, the mixer's sizes under ``mixer`` and ``mlp`` = {kind: dense, ff} or
-null), ``loop`` = {start, stop, times} (absent: every layer runs once). Every size and every constant that can
+has ``type`` = attention | mlstm | delta, the mixer's sizes under ``mixer`` (``kv_heads`` absent: as many as heads;
+the attention's ``scale`` absent: 1 / sqrt(dim); ``mask``, ``rot``, ``rot.scaling`` absent: none) and ``mlp`` =
+{kind: dense, ff} or null), ``loop`` = {start, stop, times} (absent: every layer runs once). Every size and every constant that can
 differ between two models of the design comes from here; nothing is taken from a particular checkpoint.
 """
 from __future__ import annotations
@@ -77,7 +78,7 @@ class RamosunLayer:
         heads = _positive_int(mixer, "heads", where_mixer)
         dim = _positive_int(mixer, "dim", where_mixer)
         vdim = _positive_int(mixer, "vdim", where_mixer)
-        kv_heads = heads if kind == MLSTM else _positive_int(mixer, "kv_heads", where_mixer)
+        kv_heads = heads if kind == MLSTM or mixer.get("kv_heads") is None else _positive_int(mixer, "kv_heads", where_mixer)
         if heads % kv_heads:
             raise ConfigError(f"{where_mixer}: {heads} heads are not a multiple of {kv_heads} kv_heads")
         ff = None
@@ -92,7 +93,7 @@ class RamosunLayer:
                 raise ConfigError(f"{where_mixer}: the values are the keys, so vdim {vdim} must equal dim {dim}")
             mask = mixer.get("mask")
             fields["window"] = _positive_int(mask, "size", where_mixer + ".mask") if mask is not None else None
-            fields["scale"] = float(_need(mixer, "scale", where_mixer))
+            fields["scale"] = float(mixer["scale"]) if mixer.get("scale") is not None else dim ** -0.5
             rot = mixer.get("rot")
             fields["rotary"] = RotaryConfig.from_dict(rot, dim, where_mixer + ".rot") if rot is not None else None
         elif kind == MLSTM:
