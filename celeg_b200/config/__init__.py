@@ -9,10 +9,14 @@ from .lfm2_arch import build_lfm2_spec
 from .ramosun import RamosunConfig
 from . import ramosun_arch as _ramosun_arch  # registers "Ramosun"
 from .ramosun_arch import build_ramosun_spec
+from .kedesun import KedesunConfig
+from . import kedesun_arch as _kedesun_arch  # registers "Kedesun"
+from .kedesun_arch import build_kedesun_spec
 
 __all__ = [
     "Architecture", "ConfigError", "UnknownArchitectureError", "ExecutionEntry", "LayerSpec",
     "ModelSpec", "PartSpec", "TensorRef", "architecture_named", "architecture_of",
     "known_architectures", "read_config_json", "register_architecture", "CONV",
     "FULL_ATTENTION", "Lfm2Config", "build_lfm2_spec", "RamosunConfig", "build_ramosun_spec",
+    "KedesunConfig", "build_kedesun_spec",
 ]

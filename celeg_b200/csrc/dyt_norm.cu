@@ -152,7 +152,7 @@ CELEG_API int celeg_join_stream_embedding(const float* residual, const void* del
 // out = act(in), element by element (in place allowed): 0 the exact GELU, 1 the tanh GELU, 2 SiLU
 CELEG_API int celeg_activation(const void* in, void* out, long long count, int kind, int act_dtype,
                                cudaStream_t stream) {
-    CELEG_REQUIRE(count >= 0 && kind >= 0 && kind <= 2, "activation: invalid count %lld or kind %d", count, kind);
+    CELEG_REQUIRE(count >= 0 && kind >= 0 && kind <= 3, "activation: invalid count %lld or kind %d", count, kind);
     if (count == 0) return 0;
     const int per_vector = act_dtype == kFloat32 ? 4 : 8;
     if ((act_dtype == kFloat32 || act_dtype == kBFloat16) && count % per_vector == 0 &&

@@ -509,7 +509,7 @@ CELEG_API int celeg_gemm_tcgen05(const void* a, int lda, const void* b, int ldb,
                   "gemm_tcgen05: k=%d, lda=%d and ldb=%d must be multiples of 8 and cover k", k, lda, ldb);
     CELEG_REQUIRE((((size_t)a | (size_t)b) & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
     CELEG_REQUIRE(ldc >= n && error_flag != nullptr, "gemm_tcgen05: ldc=%d is smaller than n=%d, or no error flag", ldc, n);
-    CELEG_REQUIRE(epilogue >= 0 && epilogue <= 5, "gemm_tcgen05: unknown epilogue %d", epilogue);
+    CELEG_REQUIRE(epilogue >= 0 && epilogue <= 6, "gemm_tcgen05: unknown epilogue %d", epilogue);
     CELEG_REQUIRE((m + kTileM - 1) / kTileM <= 65535, "gemm_tcgen05: %d rows exceed one launch", m);
     // Which kernel: many rows -> the persistent kernel (128 x 256 tiles, epilogue hidden under the next
     // tile); few rows -> 128 x 128 tiles with two blocks per SM, which gives more blocks to spread the

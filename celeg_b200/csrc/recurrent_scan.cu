@@ -1,5 +1,6 @@
-// Mixers whose cache is a matrix per head that every token rewrites: the mLSTM matrix memory and the gated
-// delta rule. State, gates and every sum are float32 on both precision paths.
+// Mixers whose cache is a matrix per head that every token rewrites: the mLSTM matrix memory, the gated
+// delta rule and the retention (a fixed decay per head). State, gates and every sum are float32 on both
+// precision paths.
 //
 // The recurrences, per head, with S [dim, vdim] (and for the mLSTM a normaliser n [dim] and a running
 // maximum m that starts at 0):
@@ -7,6 +8,8 @@
 //   mLSTM   m' = max(f + m, i);  a = exp(f + m - m'),  b = exp(i - m')
 //           S' = a S + b k v^T;  n' = a n + b k;  o = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6)
 //   delta   S~ = g S;  u = beta (v - S~^T k);  S' = S~ + k u^T;  o = S'^T q
+//   retention   S' = d S + k v^T;  o = S'^T q   with d a constant of the head (`gates` holds one per head, not per
+//           token); the key's factor dim^(-1/2) rides on q_scale, which is the same product
 //
 // Column j of S depends on column j alone, so a launch is cut by (span, head, run of columns) and walks the
 // span's tokens in order. A column lives in the registers of L lanes (L = 1 .. 32 by the key size, 8
@@ -27,12 +30,13 @@ constexpr int kScanWarps = 4;        // warps of a block: they share the staged 
 constexpr int kScanThreads = kScanWarps * 32;
 constexpr int kScanMaxDim = 256;
 
-enum ScanMode : int { kScanDelta = 0, kScanMlstm = 1 };
+enum ScanMode : int { kScanDelta = 0, kScanMlstm = 1, kScanRetention = 2 };
 
 struct ScanParams {
     const float* q; const float* k; const float* v;     // rows of the step's tokens; head h at h * dim (h * vdim)
     int q_stride, k_stride, v_stride;
-    const float* gates;                                  // [tokens, 2 * heads]: delta (beta, g); mLSTM (i, f), logs
+    const float* gates;                                  // [tokens, 2 * heads]: delta (beta, g); mLSTM (i, f), logs;
+                                                         // retention: [heads], the decay of each head
     float* out;                                          // [tokens, heads * vdim]
     float* state;                                        // this part's floats inside slot 0
     long long slot_stride;
@@ -103,7 +107,8 @@ __global__ void __launch_bounds__(kScanThreads) recurrent_scan_kernel(const Scan
     float m = MODE == kScanMlstm ? *m_head : 0.0f;
 
     const float* k_base = p.k + (size_t)kv_head * dim;
-    const float* q_base = p.q + (size_t)(MODE == kScanMlstm ? head : kv_head) * dim;
+    const float* q_base = p.q + (size_t)(MODE == kScanDelta ? kv_head : head) * dim;
+    const float head_decay = MODE == kScanRetention ? p.gates[head] : 0.0f;
     auto issue = [&](int t0, int stage) {
         const int count = min(kTile, t_end - t0);
         if (p.vector_copies) {
@@ -125,6 +130,7 @@ __global__ void __launch_bounds__(kScanThreads) recurrent_scan_kernel(const Scan
             const int gc = blockIdx.x * kCols + c;
             if (gc < vdim) cp_async_4(&v_s[stage][tt][c], p.v + (size_t)(t0 + tt) * p.v_stride + (size_t)head * vdim + gc);
         }
+        if (MODE != kScanRetention)
         for (int i = tid; i < count * 2; i += kScanThreads) {
             const int tt = i >> 1, w = i & 1;
             cp_async_4(&g_s[stage][tt][w], p.gates + (size_t)(t0 + tt) * 2 * p.heads + w * p.heads + head);
@@ -178,9 +184,14 @@ __global__ void __launch_bounds__(kScanThreads) recurrent_scan_kernel(const Scan
             d_kq *= p.q_scale;
             d_nq *= p.q_scale;
             const float vj = v_s[stage][tt][col_in];
-            const float g0 = g_s[stage][tt][0], g1 = g_s[stage][tt][1];
+            const float g0 = MODE == kScanRetention ? 0.0f : g_s[stage][tt][0];
+            const float g1 = MODE == kScanRetention ? 0.0f : g_s[stage][tt][1];
             float o;
-            if (MODE == kScanDelta) {
+            if (MODE == kScanRetention) {
+                o = fmaf(head_decay, d_sq, vj * d_kq);
+#pragma unroll
+                for (int r = 0; r < kScanRegs; ++r) s[r] = fmaf(kk[r], vj, head_decay * s[r]);
+            } else if (MODE == kScanDelta) {
                 const float beta = g0, decay = g1;
                 const float u = beta * (vj - decay * d_sk);
                 o = decay * d_sq + u * d_kq;
@@ -371,13 +382,13 @@ __global__ void gated_head_norm_kernel(const float* o, const float* gate, int ga
     for (int i = lane; i < vdim; i += 32) sum += src[i] * src[i];
     sum = warp_sum(sum);
     const float inv = 1.0f / sqrtf(sum / (float)vdim + eps);
-    const float* w = weight + (weight_per_head ? (size_t)h * vdim : 0);
+    const float* w = weight ? weight + (weight_per_head ? (size_t)h * vdim : 0) : nullptr;     // (null: no weight)
     const float* g = gate + (size_t)t * gate_stride + (size_t)h * vdim;
     A* dst = out + ((size_t)t * heads + h) * vdim;
     for (int i = lane; i < vdim; i += 32) {
         const float z = g[i];
         const float sig = 1.0f / (1.0f + expf(-z));
-        dst[i] = from_float<A>(src[i] * inv * w[i] * (gate_kind == 0 ? sig : z * sig));
+        dst[i] = from_float<A>(src[i] * inv * (w ? w[i] : 1.0f) * (gate_kind == 0 ? sig : z * sig));
     }
 }
 
@@ -409,7 +420,7 @@ __global__ void __launch_bounds__(256) recurrent_decode_kernel(const DecodeStepP
     const int head = blockIdx.x, t = blockIdx.y;
     const int dim = p.dim, vdim = p.vdim, heads = p.heads;
     const int kv_head = head / (heads / p.kv_heads);
-    const int qk_head = MODE == kScanMlstm ? head : kv_head;
+    const int qk_head = MODE == kScanDelta ? kv_head : head;
     float* k_s = decode_smem;
     float* q_s = k_s + dim;
     float* o_s = q_s + dim;
@@ -464,7 +475,10 @@ __global__ void __launch_bounds__(256) recurrent_decode_kernel(const DecodeStepP
     if (MODE == kScanMlstm) nq = block_sum(nq, scratch) * p.q_scale;
 
     float g0, g1, keep = 0.0f, write = 0.0f, lower = 1.0f, m_new = 0.0f;
-    if (MODE == kScanDelta) {
+    if (MODE == kScanRetention) {
+        g0 = 1.0f;
+        g1 = p.bias0[head];                                                     // the head's decay
+    } else if (MODE == kScanDelta) {
         g0 = 1.0f / (1.0f + expf(-row[p.g0_off + head]));                      // beta
         const float x = row[p.g1_off + head] + p.bias1[head];
         g1 = expf(-expf(p.bias0[head]) * (fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x)))));     // decay
@@ -532,7 +546,11 @@ __global__ void __launch_bounds__(256) recurrent_decode_kernel(const DecodeStepP
             sq *= p.q_scale;
             const float vj = MODE == kScanDelta ? convolved(p.v_off + head * vdim + j) : row[p.v_off + head * vdim + j];
             float o, scale, add;
-            if (MODE == kScanDelta) {
+            if (MODE == kScanRetention) {
+                add = vj;
+                scale = g1;
+                o = fmaf(g1, sq, vj * kq);
+            } else if (MODE == kScanDelta) {
                 add = g0 * (vj - g1 * sk);            // u
                 scale = g1;
                 o = g1 * sq + add * kq;
@@ -566,12 +584,12 @@ __global__ void __launch_bounds__(256) recurrent_decode_kernel(const DecodeStepP
     }
     squares = block_sum(squares, scratch);
     const float inv = 1.0f / sqrtf(squares / (float)vdim + p.eps);
-    const float* w = p.norm_w + (p.norm_per_head ? (size_t)head * vdim : 0);
+    const float* w = p.norm_w ? p.norm_w + (p.norm_per_head ? (size_t)head * vdim : 0) : nullptr;   // (null: no weight)
     A* dst = static_cast<A*>(p.out) + ((size_t)t * heads + head) * vdim;
     for (int j = threadIdx.x; j < vdim; j += blockDim.x) {
         const float z = row[p.gate_off + head * vdim + j];
         const float sig = 1.0f / (1.0f + expf(-z));
-        dst[j] = from_float<A>(o_s[j] * inv * w[j] * (MODE == kScanMlstm ? sig : z * sig));
+        dst[j] = from_float<A>(o_s[j] * inv * (w ? w[j] : 1.0f) * (MODE == kScanMlstm ? sig : z * sig));
     }
 }
 
@@ -600,7 +618,8 @@ static int launch_scan(const ScanParams& p, int spans, cudaStream_t stream) {
 using namespace celeg_b200;
 
 // mode 0: gated delta rule (q heads = kv_heads, gates = beta | decay); mode 1: mLSTM (q heads = heads,
-// gates = log input | log forget; the slot holds S, then n [heads, dim], then m [heads]).
+// gates = log input | log forget; the slot holds S, then n [heads, dim], then m [heads]); mode 2: retention
+// (q heads = heads, gates = one decay per head [heads]).
 CELEG_API int celeg_recurrent_scan(int mode, const float* q, int q_stride, const float* k, int k_stride, const float* v,
                                    int v_stride, const float* gates, float* out, float* state, long long slot_stride,
                                    const int* span_begin, const int* span_slot, int spans, int heads, int kv_heads,
@@ -609,13 +628,14 @@ CELEG_API int celeg_recurrent_scan(int mode, const float* q, int q_stride, const
                   "recurrent_scan: invalid sizes spans=%d heads=%d kv_heads=%d dim=%d vdim=%d", spans, heads, kv_heads,
                   dim, vdim);
     CELEG_REQUIRE(dim <= kScanMaxDim, "recurrent_scan: a key size of %d exceeds %d", dim, kScanMaxDim);
-    CELEG_REQUIRE(mode == kScanDelta || mode == kScanMlstm, "recurrent_scan: unknown mode %d", mode);
+    CELEG_REQUIRE(mode == kScanDelta || mode == kScanMlstm || mode == kScanRetention, "recurrent_scan: unknown mode %d", mode);
     CELEG_REQUIRE(spans <= 65535 && heads <= 65535, "recurrent_scan: %d spans or %d heads exceed one launch", spans, heads);
     if (spans == 0) return 0;
     const int vector_copies = dim % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 &&
                               (((size_t)q | (size_t)k) & 15) == 0;
     const ScanParams p = {q, k, v, q_stride, k_stride, v_stride, gates, out, state, slot_stride, span_begin, span_slot,
                           heads, kv_heads, dim, vdim, q_scale, vector_copies};
+    if (mode == kScanRetention) return launch_scan<kScanRetention>(p, spans, stream);
     return mode == kScanDelta ? launch_scan<kScanDelta>(p, spans, stream) : launch_scan<kScanMlstm>(p, spans, stream);
 }
 
@@ -683,6 +703,7 @@ CELEG_API int celeg_gated_head_norm(const float* o, const float* gate, int gate_
 // two projections of a matrix-state mixer in one launch. mode 0 (delta): the convolved channels [q | k | v] are
 // the first ``channels`` columns of a row, bias0 = A_log, bias1 = dt_bias, the output gate is SiLU; the carried
 // inputs are moved on by a second launch. mode 1 (mLSTM): bias0 / bias1 = the gates' biases, the gate is a sigmoid.
+// mode 2 (retention): bias0 = the heads' decays, the output gate is SiLU, norm_w may be null (no weight).
 CELEG_API int celeg_recurrent_decode(int mode, const float* proj, int stride, int q_off, int k_off, int v_off,
                                      int gate_off, int g0_off, int g1_off, const float* conv_kernel, float* carried,
                                      int taps, int channels, const float* bias0, const float* bias1, float cap,
@@ -693,8 +714,8 @@ CELEG_API int celeg_recurrent_decode(int mode, const float* proj, int stride, in
     CELEG_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0,
                   "recurrent_decode: invalid sizes tokens=%d heads=%d kv_heads=%d dim=%d vdim=%d", tokens, heads,
                   kv_heads, dim, vdim);
-    CELEG_REQUIRE(mode == kScanDelta || mode == kScanMlstm, "recurrent_decode: unknown mode %d", mode);
-    CELEG_REQUIRE(mode == kScanMlstm || (taps >= 1 && taps <= 16 && conv_kernel && (taps == 1 || carried)),
+    CELEG_REQUIRE(mode == kScanDelta || mode == kScanMlstm || mode == kScanRetention, "recurrent_decode: unknown mode %d", mode);
+    CELEG_REQUIRE(mode != kScanDelta || (taps >= 1 && taps <= 16 && conv_kernel && (taps == 1 || carried)),
                   "recurrent_decode: the delta rule needs its kernel of 1 to 16 taps and the carried inputs");
     CELEG_REQUIRE(act_dtype == kFloat32 || act_dtype == kBFloat16, "recurrent_decode: unknown dtype code %d", act_dtype);
     CELEG_REQUIRE(tokens <= 65535, "recurrent_decode: %d tokens exceed one launch", tokens);
@@ -717,6 +738,13 @@ CELEG_API int celeg_recurrent_decode(int mode, const float* proj, int stride, in
         launch_chained(carried_inputs_update_kernel, (unsigned)((units + 127) / 128), 128, 0, stream, proj, stride,
                        carried, slot_stride, span_begin, span_slot, tokens, channels, taps);
         return check_launch("carried_inputs_update");
+    }
+    if (mode == kScanRetention) {
+        if (act_dtype == kFloat32)
+            launch_chained(recurrent_decode_kernel<kScanRetention, float>, grid, kDecodeStepThreads, smem, stream, p);
+        else
+            launch_chained(recurrent_decode_kernel<kScanRetention, __nv_bfloat16>, grid, kDecodeStepThreads, smem, stream, p);
+        return check_launch("recurrent_decode");
     }
     if (act_dtype == kFloat32)
         launch_chained(recurrent_decode_kernel<kScanMlstm, float>, grid, kDecodeStepThreads, smem, stream, p);

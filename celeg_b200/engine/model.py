@@ -193,8 +193,14 @@ class Model:
             stream.after_layer = firsts[position + 1] if position + 1 < len(blocks) else head_norm
             if position + 1 < len(blocks) and self.order[position + 1].before:
                 stream.after_layer = None           # (a stream part reads the stream next, not that block's norm)
+            # what the next block asks of the stream first (a stream part after this block may write it already)
+            stream.upcoming = None
+            if position + 1 < len(blocks) and not self.order[position + 1].before:
+                entry = getattr(blocks[position + 1], "entry_norm", None)
+                stream.upcoming = entry() if entry is not None else None
             layer.block.run(stream, step)
         stream.after_layer = None
+        stream.upcoming = None
         if n_logits == 0:
             stream.prepared = None
             return

@@ -103,6 +103,23 @@ _SIGNATURES = {
                             c_int, c_float, c_void_p],
     "celeg_gated_head_norm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_int,
                               c_int, c_void_p],
+    "celeg_depth_average": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
+                            c_float, c_int, c_int, c_int, c_void_p],
+    "celeg_latent_prepare": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p,
+                             c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                             c_int, c_int, c_void_p, c_int, c_void_p],
+    "celeg_head_project": [c_void_p, c_int, c_int, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_int, c_int,
+                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "celeg_head_gate": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "celeg_moe_route": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                        c_int, c_int, c_void_p],
+    "celeg_moe_group": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "celeg_expert_product": [c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_int,
+                             c_int, c_int, c_int, c_int, c_void_p],
+    "celeg_expert_rows": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int,
+                          c_int, c_int, c_int, c_void_p],
+    "celeg_moe_combine": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                          c_void_p],
 }
 
 
@@ -371,7 +388,7 @@ def attention_prefill_tcgen05(q: torch.Tensor, q_row_stride: int, out: torch.Ten
         head_dim, page_tokens, int(window or 0), scale, _ptr(sinks), _ptr(error_flag), _stream()))
 
 
-ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU = 0, 1, 2      # codes of csrc/common.cuh: activate()
+ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU, ACT_RELU_SQUARED = 0, 1, 2, 3      # codes of csrc/common.cuh: activate()
 GEMV_MAX_ROWS = 16
 GEMV_STORE, GEMV_STORE_F32, GEMV_ADD_RESIDUAL, GEMV_SWIGLU, GEMV_CONV, GEMV_ACTIVATION = 0, 1, 2, 3, 4, 5
 
@@ -568,7 +585,7 @@ def softcap(logits: torch.Tensor, rows: int, cap: float) -> None:
     _check(library().celeg_softcap(_ptr(logits), rows * logits.shape[1], cap, _stream()))
 
 
-SCAN_DELTA, SCAN_MLSTM = 0, 1
+SCAN_DELTA, SCAN_MLSTM, SCAN_RETENTION = 0, 1, 2
 SCAN_MAX_DIM = 256
 
 
@@ -576,11 +593,13 @@ def recurrent_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                    state: torch.Tensor, slot_stride: int, span_begin: torch.Tensor, span_slot: torch.Tensor, spans: int,
                    heads: int, kv_heads: int, dim: int, vdim: int, q_scale: float) -> None:
     """The matrix-state recurrences of csrc/recurrent_scan.cu over the step's spans. q, k, v: float32 column
-    views of [tokens, *] buffers (row strides are taken from them); gates float32 [tokens, 2*heads]; out float32
+    views of [tokens, *] buffers (row strides are taken from them); gates float32 [tokens, 2*heads] (retention:
+    [heads], each head's decay); out float32
     [tokens, heads*vdim]; ``state`` points at this part's floats inside slot 0."""
     for tensor in (q, k, v, gates, out, state):
         assert tensor.dtype == torch.float32 and tensor.stride(-1) == 1
-    assert gates.is_contiguous() and out.is_contiguous() and gates.shape[1] == 2 * heads and out.shape[1] == heads * vdim
+    assert gates.is_contiguous() and out.is_contiguous() and out.shape[1] == heads * vdim
+    assert gates.shape == (heads,) if mode == SCAN_RETENTION else gates.shape[1] == 2 * heads
     _check(library().celeg_recurrent_scan(mode, _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0),
                                           _ptr(gates), _ptr(out), _ptr(state), slot_stride, _ptr(span_begin),
                                           _ptr(span_slot), spans, heads, kv_heads, dim, vdim, q_scale, _stream()))
@@ -634,10 +653,137 @@ def delta_prepare(proj: torch.Tensor, kernel: torch.Tensor, carried: torch.Tenso
 GATE_SIGMOID, GATE_SILU = 0, 1
 
 
-def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, weight_per_head: bool, out: torch.Tensor,
-                    tokens: int, heads: int, vdim: int, eps: float, gate_kind: int) -> None:
-    """out = o / sqrt(mean_head(o^2) + eps) * weight * act(gate) per (token, head); o and gate float32."""
+def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], weight_per_head: bool,
+                    out: torch.Tensor, tokens: int, heads: int, vdim: int, eps: float, gate_kind: int) -> None:
+    """out = o / sqrt(mean_head(o^2) + eps) * weight * act(gate) per (token, head); o and gate float32; ``weight``
+    None: no weight."""
     assert o.dtype == torch.float32 and gate.dtype == torch.float32 and o.is_contiguous() and gate.stride(-1) == 1
     _check(library().celeg_gated_head_norm(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), int(weight_per_head),
                                            _ptr(out), tokens, heads, vdim, eps, gate_kind, dtype_code(out.dtype),
                                            _stream()))
+
+
+# ------------------------------------------- depth average, latent attention, mixture of experts
+def depth_average(stream: torch.Tensor, delta_a: Optional[torch.Tensor], delta_b: Optional[torch.Tensor],
+                  history: torch.Tensor, weights: torch.Tensor, index: int, n_rows: int,
+                  norm_weight: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, eps: float = 0.0) -> None:
+    """X_(index+1) = stream (+ deltas) goes into ``history`` (float32 [entries, rows, width]; block 0 also stores its
+    input as X_0), the stream becomes sum_j weights[j] X_j, and with ``norm_weight`` its RMSNorm is written to ``out``."""
+    _need(stream, torch.float32, "stream")
+    _need(history, torch.float32, "history")
+    _need(weights, torch.float32, "weights")
+    width = stream.shape[-1]
+    assert history.shape[0] >= index + 2 and history.shape[-1] == width and weights.numel() == index + 2
+    given = delta_a if delta_a is not None else delta_b
+    act = out.dtype if out is not None else (given.dtype if given is not None else torch.float32)
+    for delta in (delta_a, delta_b):
+        assert delta is None or (delta.dtype == act and delta.shape[-1] == width and delta.is_contiguous())
+    _check(library().celeg_depth_average(_ptr(stream), _ptr(delta_a), _ptr(delta_b), _ptr(history), history.stride(0),
+                                         _ptr(weights), index, _ptr(norm_weight), _ptr(out), eps, n_rows, width,
+                                         dtype_code(act), _stream()))
+
+
+def latent_prepare(q: torch.Tensor, down: torch.Tensor, norm_weight: torch.Tensor, frequencies: torch.Tensor,
+                   magnitude: float, eps: float, positions: torch.Tensor, token_span: torch.Tensor,
+                   block_table: torch.Tensor, cache: torch.Tensor, page_tokens: int, query: torch.Tensor, tokens: int,
+                   heads: int, dim: int, rot: int, rotated: int, rank: int, error_flag: torch.Tensor) -> None:
+    """The latent attention's token-parallel step (csrc/latent_attention.cu): the normalised latent vector and the
+    rotated shared key part go to the token's place in ``cache`` (pages of [page_tokens, rank + rot]), every head's
+    rotated query part to ``query[t, h, rank:]`` ([tokens, heads * (rank + rot)]). Of the ``rot`` dimensions of a
+    rotated part the first ``rotated`` turn (pairs of neighbours), the rest pass unchanged."""
+    assert q.dtype == down.dtype == cache.dtype == query.dtype and q.stride(-1) == 1 and down.stride(-1) == 1
+    assert query.stride(-1) == 1 and cache.is_contiguous()
+    _check(library().celeg_latent_prepare(
+        _ptr(q), q.stride(0), _ptr(down), down.stride(0), _ptr(norm_weight), _ptr(frequencies), magnitude, eps,
+        _ptr(positions), _ptr(token_span), _ptr(block_table), block_table.stride(0), _ptr(cache), cache.stride(0),
+        page_tokens, _ptr(query), query.stride(0), tokens, heads, dim, rot, rotated, rank, _ptr(error_flag), dtype_code(q.dtype),
+        _stream()))
+
+
+def head_project(x: torch.Tensor, in_head: int, matrix: torch.Tensor, contract_rows: bool, out: torch.Tensor,
+                 out_head: int, tokens: int, heads: int, n: int, k: int, gate: Optional[torch.Tensor] = None) -> None:
+    """out[t, h * out_head + j] = sum_i x[t, h * in_head + i] M_h[i, j] (times sigmoid(gate[t, h])) for j < n, i < k.
+    ``matrix`` is a stored projection [heads * rows, columns]: with ``contract_rows`` M_h[i, j] = matrix[h * k + i, j]
+    (the sum runs over the head's rows), else M_h[i, j] = matrix[h * n + j, i] (over its columns)."""
+    assert x.dtype == matrix.dtype == out.dtype and x.stride(-1) == 1 and out.stride(-1) == 1 and matrix.is_contiguous()
+    columns = matrix.shape[1]
+    if contract_rows:
+        m_head, m_k, m_n = k * columns, columns, 1
+    else:
+        m_head, m_k, m_n = n * columns, 1, columns
+    if gate is not None:
+        assert gate.dtype == x.dtype and gate.stride(-1) == 1
+    _check(library().celeg_head_project(_ptr(x), x.stride(0), in_head, _ptr(matrix), m_head, m_k, m_n, _ptr(out),
+                                        out.stride(0), out_head, _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                        tokens, heads, n, k, dtype_code(x.dtype), _stream()))
+
+
+def head_gate(values: torch.Tensor, head_width: int, gate: torch.Tensor, tokens: int, heads: int) -> None:
+    """values[t, h * head_width + j] *= sigmoid(gate[t, h]), in place."""
+    assert values.dtype == gate.dtype and values.stride(-1) == 1 and gate.stride(-1) == 1
+    _check(library().celeg_head_gate(_ptr(values), values.stride(0), head_width, _ptr(gate), gate.stride(0), tokens,
+                                     heads, dtype_code(values.dtype), _stream()))
+
+
+MOE_TILE = 64
+
+
+def moe_max_tiles(pairs: int, experts: int) -> int:
+    """The most row tiles that ``pairs`` (token, choice) pairs can make, however they fall on the experts."""
+    return pairs // MOE_TILE + min(pairs, experts)
+
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor],
+              shared_gate_weight: Optional[torch.Tensor], chosen: torch.Tensor, weights: torch.Tensor,
+              shared_gate: Optional[torch.Tensor], tokens: int, top: int) -> None:
+    """chosen int32 [tokens, top], weights float32 [tokens, top]: the ``top`` experts with the largest
+    softmax(router h) + correction and their softmax scores divided by their sum; shared_gate float32 [tokens] =
+    sigmoid(shared_gate_weight . h). Sums in float32."""
+    _need(router, torch.float32, "router")
+    experts, width = router.shape
+    assert h.stride(-1) == 1 and h.shape[-1] == width and chosen.dtype == torch.int32 and weights.dtype == torch.float32
+    _check(library().celeg_moe_route(_ptr(h), h.stride(0), _ptr(router), _ptr(correction), _ptr(shared_gate_weight),
+                                     _ptr(chosen), _ptr(weights), _ptr(shared_gate), tokens, width, experts, top,
+                                     dtype_code(h.dtype), _stream()))
+
+
+def moe_group(chosen: torch.Tensor, tokens: int, experts: int, top: int, place_of_pair: torch.Tensor,
+              source_of_place: torch.Tensor, table: torch.Tensor) -> None:
+    """Orders the (token, choice) pairs by expert: place_of_pair [tokens * top], source_of_place [tokens * top] (the
+    token of each place) and the tile table int32 [4 + 3 * moe_max_tiles] (count, then (expert, first place, rows))."""
+    assert table.numel() >= 4 + 3 * moe_max_tiles(tokens * top, experts)
+    _check(library().celeg_moe_group(_ptr(chosen), tokens, experts, top, _ptr(place_of_pair), _ptr(source_of_place),
+                                     _ptr(table), _stream()))
+
+
+def expert_product(x: torch.Tensor, source: Optional[torch.Tensor], weights: torch.Tensor, out: torch.Tensor,
+                   table: torch.Tensor, max_tiles: int, activation: int) -> None:
+    """out[place] = act(x[source[place]] @ weights[expert of the place]^T) over the tile table; ``weights``
+    [experts, n, k]; ``activation`` a code of ACT_* or -1."""
+    assert x.dtype == weights.dtype == out.dtype and weights.is_contiguous() and x.stride(-1) == 1 and out.stride(-1) == 1
+    _, n, k = weights.shape
+    _check(library().celeg_expert_product(_ptr(x), x.stride(0), _ptr(source), _ptr(weights), weights.stride(0),
+                                          weights.stride(1), _ptr(out), out.stride(0), _ptr(table), max_tiles, n, k,
+                                          activation, dtype_code(x.dtype), _stream()))
+
+
+def expert_rows(x: torch.Tensor, pairs_per_row: int, chosen: torch.Tensor, weights: torch.Tensor, out: torch.Tensor,
+                pairs: int, activation: int) -> None:
+    """out[pair] = act(x[pair // pairs_per_row] @ weights[chosen[pair]]^T) for few pairs (the weights stream once)."""
+    assert x.dtype == weights.dtype == out.dtype and weights.is_contiguous() and x.stride(-1) == 1 and out.stride(-1) == 1
+    _, n, k = weights.shape
+    _check(library().celeg_expert_rows(_ptr(x), x.stride(0), pairs_per_row, _ptr(chosen), _ptr(weights),
+                                       weights.stride(0), weights.stride(1), _ptr(out), out.stride(0), pairs, n, k,
+                                       activation, dtype_code(x.dtype), _stream()))
+
+
+def moe_combine(expert_out: torch.Tensor, place_of_pair: Optional[torch.Tensor], weights: torch.Tensor,
+                shared: Optional[torch.Tensor], shared_gate: Optional[torch.Tensor], y: torch.Tensor, tokens: int,
+                top: int) -> None:
+    """y[t] = sum_k weights[t, k] expert_out[place_of_pair[t * top + k]] (+ shared_gate[t] shared[t])."""
+    width = y.shape[-1]
+    assert expert_out.dtype == y.dtype and expert_out.stride(-1) == 1 and y.is_contiguous()
+    assert shared is None or (shared.dtype == y.dtype and shared.is_contiguous() and shared.shape[-1] == width)
+    _check(library().celeg_moe_combine(_ptr(expert_out), expert_out.stride(0), _ptr(place_of_pair), _ptr(weights),
+                                       _ptr(shared), _ptr(shared_gate), _ptr(y), tokens, width, top,
+                                       dtype_code(y.dtype), _stream()))

@@ -2,7 +2,7 @@
 from .registry import CATEGORIES, part_factory, register_part, registered
 from .options import KernelOptions
 from .runtime import Runtime, StepContext
-from . import norms, positions, mixers, recurrent, feed_forward, arrangement, ends, stream_parts  # register the built-in kinds
+from . import norms, positions, mixers, recurrent, latent, feed_forward, arrangement, ends, stream_parts  # register the built-in kinds
 from .mixers import AttentionMixer, PagedBinding, ShortConvMixer, StateBinding
 from .norms import DynamicTanh, RmsNorm
 from .recurrent import GatedDeltaMixer, MlstmMixer

@@ -63,7 +63,9 @@ class PreNormResidual:
 class ParallelResidual:
     """y = x + Mixer(Norm_1(x)) + FeedForward(Norm_2(x)): both read the same x, each through its own norm, and
     both outputs are owed to the stream together (added inside the next block's norm pass). Without a
-    feed-forward: y = x + Mixer(Norm_1(x))."""
+    feed-forward: y = x + Mixer(Norm_1(x)). A block that names a feed-forward but no second norm has ONE norm whose
+    output both read: y = x + Mixer(h) + FeedForward(h), h = Norm_1(x). A stream part under the name ``after``
+    among the layer's parts runs when both outputs are owed (it settles them itself)."""
 
     def __init__(self, layer_parts: Mapping, rt: Runtime):
         self.rt = rt
@@ -71,11 +73,16 @@ class ParallelResidual:
         self.mixer = layer_parts["mixer"]
         self.ffn_norm = layer_parts.get("feed_forward_norm")
         self.ffn = layer_parts.get("feed_forward")
+        self.after = layer_parts.get("after")
         hidden = self.mixer_norm.width
         self.normed_a = rt.scratch("block.normed", hidden)
-        self.normed_b = rt.scratch("block.normed_b", hidden)
+        self.normed_b = rt.scratch("block.normed_b", hidden) if self.ffn_norm is not None else None
         self.delta_a = rt.scratch("block.delta_a", hidden)
         self.delta_b = rt.scratch("block.delta_b", hidden)
+
+    def entry_norm(self):
+        """(norm, buffer) of the first thing run() asks of the stream: that norm of every row, into that buffer."""
+        return self.mixer_norm, self.normed_a
 
     def run(self, stream: ResidualStream, step: StepContext) -> None:
         stream.expect(self.delta_a, None, step.tokens)
@@ -83,8 +90,13 @@ class ParallelResidual:
             x = stream.normed(self.mixer_norm, self.normed_a, step.tokens)
             self.mixer.forward(x, self.delta_a, step)
             stream.add_later(self.delta_a)
+            if self.after is not None:
+                self.after.run(stream, step)
             return
-        x_mixer, x_ffn = stream.normed_pair(self.mixer_norm, self.normed_a, self.ffn_norm, self.normed_b, step.tokens)
+        if self.ffn_norm is None:
+            x_mixer = x_ffn = stream.normed(self.mixer_norm, self.normed_a, step.tokens)
+        else:
+            x_mixer, x_ffn = stream.normed_pair(self.mixer_norm, self.normed_a, self.ffn_norm, self.normed_b, step.tokens)
         rt = self.rt
         if rt.side_by_side_branches and rt.small_batch(step.tokens):
             # few rows: both chains are short kernels that leave most of the GPU idle, and they share nothing but
@@ -105,3 +117,5 @@ class ParallelResidual:
             self.ffn.forward(x_ffn, self.delta_b, step)
         stream.add_later(self.delta_a)
         stream.add_later_beside(self.delta_b)
+        if self.after is not None:
+            self.after.run(stream, step)

@@ -43,10 +43,11 @@ class SwiGluFeedForward:
 
 @register_part("feed_forward", "dense")
 class DenseFeedForward:
-    """down(act(up(x))) with act one of ``gelu`` (exact, by erf), ``gelu_tanh`` or ``silu``; the activation in
-    float32, rounded once."""
+    """down(act(up(x))) with act one of ``gelu`` (exact, by erf), ``gelu_tanh``, ``silu`` or ``relu2`` (the square of
+    ReLU); the activation in float32, rounded once."""
 
-    ACTIVATIONS = {"gelu": kernels.ACT_GELU_ERF, "gelu_tanh": kernels.ACT_GELU_TANH, "silu": kernels.ACT_SILU}
+    ACTIVATIONS = {"gelu": kernels.ACT_GELU_ERF, "gelu_tanh": kernels.ACT_GELU_TANH, "silu": kernels.ACT_SILU,
+                   "relu2": kernels.ACT_RELU_SQUARED}
 
     def __init__(self, params: Mapping, weights: Mapping[str, torch.Tensor], parts: Mapping, rt: Runtime):
         self.rt = rt
@@ -66,3 +67,69 @@ class DenseFeedForward:
         rt, t = self.rt, step.tokens
         rt.linear_activation(x, self.w_up, self.raised, t, self.activation)
         rt.linear(self.raised, self.w_down, out, t)
+
+
+@register_part("feed_forward", "moe")
+class MoeFeedForward:
+    """A mixture of ``experts`` small feed-forwards down_e(act(up_e(x))) of which each token uses ``top``:
+    s = softmax(W_router x) over all experts (float32), the experts with the largest s + ``correction`` are
+    chosen, their weights are their s divided by the sum of the chosen s (+ 1e-20), and the output is the weighted
+    sum of their outputs. A nested part ``shared`` (any feed-forward) runs for every token and is added, times
+    sigmoid(w_shared_gate . x) when the tensor ``shared_gate`` is given.
+
+    Steps of few tokens stream the chosen experts' matrices once per (token, choice) pair; larger steps order the
+    pairs by expert on the device and run both products tile by tile over a table the device makes, on a grid
+    sized for the worst case, so that nothing on the host depends on the routing (kernels: csrc/moe.cu)."""
+
+    FEW_TOKENS = 16
+
+    def __init__(self, params: Mapping, weights: Mapping[str, torch.Tensor], parts: Mapping, rt: Runtime):
+        self.rt = rt
+        self.hidden = int(params["hidden_size"])
+        self.inner = int(params["intermediate_size"])
+        self.experts = int(params["experts"])
+        self.top = int(params["top"])
+        name = params.get("activation", "relu2")
+        if name not in DenseFeedForward.ACTIVATIONS:
+            raise ValueError(f"moe: unknown activation {name!r}; known: {', '.join(DenseFeedForward.ACTIVATIONS)}")
+        self.activation = DenseFeedForward.ACTIVATIONS[name]
+        if not 0 < self.top <= self.experts:
+            raise ValueError(f"moe: top {self.top} of {self.experts} experts")
+        self.router = rt.vector(weights["router"])
+        self.correction = rt.vector(weights["correction"]) if "correction" in weights else None
+        self.shared_gate_weight = rt.vector(weights["shared_gate"].reshape(-1)) if "shared_gate" in weights else None
+        self.w_up = rt.matrix(torch.stack([weights[f"e{e}.up"] for e in range(self.experts)]))        # [E, inner, hidden]
+        self.w_down = rt.matrix(torch.stack([weights[f"e{e}.down"] for e in range(self.experts)]))    # [E, hidden, inner]
+        self.shared = parts.get("shared")
+        pairs = rt.max_tokens * self.top
+        self.max_pairs = pairs
+        self.chosen = rt.flat_scratch("moe.chosen", pairs, torch.int32)
+        self.weights = rt.flat_scratch("moe.weights", pairs, torch.float32)
+        self.shared_gate = rt.flat_scratch("moe.shared_gate", rt.max_tokens, torch.float32)
+        self.place = rt.flat_scratch("moe.place", pairs, torch.int32)
+        self.source = rt.flat_scratch("moe.source", pairs, torch.int32)
+        self.table = rt.flat_scratch("moe.table", 4 + 3 * kernels.moe_max_tiles(pairs, self.experts), torch.int32, zero=True)
+        self.raised = rt.flat_scratch("moe.raised", pairs * self.inner, rt.act_dtype).view(pairs, self.inner)
+        self.lowered = rt.flat_scratch("moe.lowered", pairs * self.hidden, rt.act_dtype).view(pairs, self.hidden)
+        self.shared_out = rt.scratch("moe.shared_out", self.hidden) if self.shared is not None else None
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
+        t, top = step.tokens, self.top
+        pairs = t * top
+        gated = self.shared is not None and self.shared_gate_weight is not None
+        kernels.moe_route(x, self.router, self.correction, self.shared_gate_weight if gated else None, self.chosen,
+                          self.weights, self.shared_gate if gated else None, t, top)
+        if self.shared is not None:
+            self.shared.forward(x, self.shared_out, step)
+        if t <= self.FEW_TOKENS:
+            kernels.expert_rows(x, top, self.chosen, self.w_up, self.raised, pairs, self.activation)
+            kernels.expert_rows(self.raised, 1, self.chosen, self.w_down, self.lowered, pairs, -1)
+            place = None
+        else:
+            kernels.moe_group(self.chosen, t, self.experts, top, self.place, self.source, self.table)
+            tiles = kernels.moe_max_tiles(pairs, self.experts)
+            kernels.expert_product(x, self.source, self.w_up, self.raised, self.table, tiles, self.activation)
+            kernels.expert_product(self.raised, None, self.w_down, self.lowered, self.table, tiles, -1)
+            place = self.place
+        kernels.moe_combine(self.lowered, place, self.weights, self.shared_out, self.shared_gate if gated else None,
+                            out, t, top)

@@ -9,6 +9,8 @@ float32 results.
     gated_delta   S' = g S + k (beta (v - (g S)^T k))^T, read-out S'^T q, after short causal convolutions with
                   SiLU on q, k, v and unit-length q, k (Yang, Kautz, Hatamizadeh, "Gated Delta Networks:
                   Improving Mamba2 with Delta Rule", 2024)
+    retention     S' = d S + k v^T with a constant decay d per head, read-out S'^T q, no softmax and no denominator
+                  (Sun et al., "Retentive Network: A Successor to Transformer for Large Language Models", 2023)
 """
 from __future__ import annotations
 
@@ -183,5 +185,70 @@ class GatedDeltaMixer:
                                step.span_begin, step.span_slot, step.spans, self.heads, self.kv_heads, self.dim,
                                self.vdim, self.dim ** -0.5)
         kernels.gated_head_norm(self.read, gate, self.norm, False, self.gated, t, self.heads, self.vdim, self.eps,
+                                kernels.GATE_SILU)
+        rt.linear(self.gated, self.w_out, out, t)
+
+
+@register_part("mixer", "retention")
+class RetentionMixer:
+    """q = W_q x, k = W_k x / sqrt(dim) (heads x dim), v = W_v x (heads x vdim); per head S <- decay_h S + k v^T
+    and the read-out S^T q, with ``decay`` one constant a head. Each head's read-out is divided by its root mean
+    square (no weight), the heads are gated by SiLU(W_g x) and projected by W_o. Per-request state: S per head,
+    float32, zero for a new request."""
+
+    def __init__(self, params: Mapping, weights: Mapping[str, torch.Tensor], parts: Mapping, rt: Runtime):
+        self.rt = rt
+        self.hidden = int(params["hidden_size"])
+        self.heads = int(params["heads"])
+        self.dim = int(params["dim"])
+        self.vdim = int(params["vdim"])
+        self.eps = float(params["eps"])
+        decay = [float(d) for d in params["decay"]]
+        if len(decay) != self.heads:
+            raise ValueError(f"retention: {len(decay)} decays for {self.heads} heads")
+        if self.dim > kernels.SCAN_MAX_DIM:
+            raise ValueError(f"retention: a key size of {self.dim} exceeds {kernels.SCAN_MAX_DIM}")
+        self.decay = torch.tensor(decay, dtype=torch.float32, device=rt.device)
+        self.qk_width = self.heads * self.dim
+        self.v_width = self.heads * self.vdim
+        fused = torch.cat([weights["q"], weights["k"], weights["v"], weights["gate"]], dim=0)
+        self.w_in = rt.matrix(fused)
+        self.w_out = rt.matrix(weights["out"])
+        self.proj_width = int(fused.shape[0])
+        self.binding: Optional[StateBinding] = None
+        self.projected = rt.scratch("recurrent.proj", self.proj_width, torch.float32)
+        self.read = rt.scratch("recurrent.read", self.v_width, torch.float32)
+        self.gated = rt.scratch("recurrent.gated", self.v_width)
+
+    def cache_need(self):
+        return StateNeed(elements=self.heads * self.dim * self.vdim)
+
+    def bind_cache(self, binding: StateBinding) -> None:
+        self.binding = binding
+
+    ends_with_product = True      # forward() writes `out` last, with rt.linear
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
+        rt, t, b = self.rt, step.tokens, self.binding
+        rt.linear(x, self.w_in, self.projected, t)
+        rows = self.projected
+        width = self.qk_width
+        if step.max_span == 1 and step.spans == t:
+            # every request brings one token: state update, read-out, head norm and output gate in one launch
+            offsets = (0, width, 2 * width, 2 * width + self.v_width, 0, 0)
+            kernels.recurrent_decode(kernels.SCAN_RETENTION, rows, offsets, None, None, 0, 0, self.decay, self.decay,
+                                     0.0, None, False, self.eps, 0.0, b.state, b.slot_stride, step.span_begin,
+                                     step.span_slot, t, self.heads, self.heads, self.dim, self.vdim, self.dim ** -0.5,
+                                     self.gated)
+            rt.linear(self.gated, self.w_out, out, t)
+            return
+        q = rows[:, :width]
+        k = rows[:, width:2 * width]
+        v = rows[:, 2 * width:2 * width + self.v_width]
+        gate = rows[:, 2 * width + self.v_width:]
+        kernels.recurrent_scan(kernels.SCAN_RETENTION, q, k, v, self.decay, self.read, b.state, b.slot_stride,
+                               step.span_begin, step.span_slot, step.spans, self.heads, self.heads, self.dim,
+                               self.vdim, self.dim ** -0.5)
+        kernels.gated_head_norm(self.read, gate, None, False, self.gated, t, self.heads, self.vdim, self.eps,
                                 kernels.GATE_SILU)
         rt.linear(self.gated, self.w_out, out, t)

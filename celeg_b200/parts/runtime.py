@@ -41,6 +41,10 @@ class ResidualStream:
                                                          # feed-forward sit side by side); only beside ``pending``
         self.prepared = None                    # (norm, SplitNorm) left by the last product
         self.after_layer = None                 # the norm after the layer being run, if its reader takes a split norm
+        # (norm, buffer) that the block after the one being run will ask for first, for every row of the step; a
+        # stream part that runs after a block may write that norm's output itself and say so in ``ready``
+        self.upcoming = None
+        self.ready = None
         self.pieces = (hidden + 15) // 16
         if rt.act_dtype == torch.bfloat16:
             self.xw = rt.scratch("stream.split_norm", hidden, torch.bfloat16)
@@ -51,6 +55,8 @@ class ResidualStream:
         self.pending_b = None
         self.prepared = None
         self.after_layer = None
+        self.upcoming = None
+        self.ready = None
         self.rt.sink = None
 
     def split(self, norm, pieces: int):
@@ -71,6 +77,11 @@ class ResidualStream:
             if prepared_norm is norm and gather is None:
                 return split
             raise RuntimeError("a norm was prepared for another reader than the one that asks")
+        if self.ready is not None:
+            ready_norm, ready_out = self.ready
+            self.ready = None
+            if ready_norm is norm and ready_out is out and gather is None and self.pending is None:
+                return out                      # (a stream part wrote this norm's rows in its own pass)
         if self.pending_b is not None and not getattr(norm, "adds_two", False):
             if gather is not None:
                 raise RuntimeError("two outputs are owed to the stream and the norm that gathers rows adds one")

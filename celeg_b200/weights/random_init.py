@@ -18,7 +18,7 @@ from .safetensors_io import write_safetensors
 
 # (mean, standard deviation); "fan_in": N(0, 1 / columns), which keeps activations of order one at any width
 _DISTRIBUTIONS = {"linear": (0.0, 0.02), "norm": (1.0, 0.05), "conv": (0.0, 0.1), "small": (0.0, 0.3),
-                  "alpha": (0.7, 0.05), "taps": (0.0, 0.5), "fan_in": (0.0, None)}
+                  "alpha": (0.7, 0.05), "taps": (0.0, 0.5), "fan_in": (0.0, None), "depth": (0.4, 0.2), "tiny": (0.0, 0.05)}
 
 
 def _generator(seed: int, name: str) -> torch.Generator:
