@@ -9,7 +9,8 @@
 //           S' = a S + b k v^T;  n' = a n + b k;  o = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6)
 //   delta   S~ = g S;  u = beta (v - S~^T k);  S' = S~ + k u^T;  o = S'^T q
 //   retention   S' = d S + k v^T;  o = S'^T q   with d a constant of the head (`gates` holds one per head, not per
-//           token); the key's factor dim^(-1/2) rides on q_scale, which is the same product
+//           token) and k the projected key times q_scale (dim^(-1/2)): the factor is applied to the value that is
+//           written and to k.q, so S is the sum of scaled keys
 //
 // Column j of S depends on column j alone, so a launch is cut by (span, head, run of columns) and walks the
 // span's tokens in order. A column lives in the registers of L lanes (L = 1 .. 32 by the key size, 8
@@ -180,7 +181,7 @@ __global__ void __launch_bounds__(kScanThreads) recurrent_scan_kernel(const Scan
                 d_kq += __shfl_xor_sync(0xffffffffu, d_kq, offset);
                 if (MODE == kScanMlstm) d_nq += __shfl_xor_sync(0xffffffffu, d_nq, offset);
             }
-            d_sq *= p.q_scale;
+            if (MODE != kScanRetention) d_sq *= p.q_scale;      // (retention: the factor is the key's, so S holds it)
             d_kq *= p.q_scale;
             d_nq *= p.q_scale;
             const float vj = v_s[stage][tt][col_in];
@@ -189,8 +190,9 @@ __global__ void __launch_bounds__(kScanThreads) recurrent_scan_kernel(const Scan
             float o;
             if (MODE == kScanRetention) {
                 o = fmaf(head_decay, d_sq, vj * d_kq);
+                const float vs = vj * p.q_scale;
 #pragma unroll
-                for (int r = 0; r < kScanRegs; ++r) s[r] = fmaf(kk[r], vj, head_decay * s[r]);
+                for (int r = 0; r < kScanRegs; ++r) s[r] = fmaf(kk[r], vs, head_decay * s[r]);
             } else if (MODE == kScanDelta) {
                 const float beta = g0, decay = g1;
                 const float u = beta * (vj - decay * d_sk);
@@ -543,11 +545,11 @@ __global__ void __launch_bounds__(256) recurrent_decode_kernel(const DecodeStepP
                 sk += part_s[w * 32 + lane];
                 sq += part_s[(warps + w) * 32 + lane];
             }
-            sq *= p.q_scale;
+            if (MODE != kScanRetention) sq *= p.q_scale;
             const float vj = MODE == kScanDelta ? convolved(p.v_off + head * vdim + j) : row[p.v_off + head * vdim + j];
             float o, scale, add;
             if (MODE == kScanRetention) {
-                add = vj;
+                add = vj * p.q_scale;                 // the key's factor: S holds scaled keys
                 scale = g1;
                 o = fmaf(g1, sq, vj * kq);
             } else if (MODE == kScanDelta) {
