@@ -35,6 +35,11 @@ struct TcGemmParams {
     int ldc;
     int* error_flag;
     int activation;        // kTcActivation: which (common.cuh)
+    // Grouped product (null: plain): B holds one [group_rows, k] matrix per group, one after the other, and the
+    // device-made table (int32: [0] tiles, then from [4] on (group, first row of A and C, rows) per tile) says which
+    // rows of A meet which group; blockIdx.y is the tile, blocks beyond the table's count leave at once.
+    const int* table;
+    int group_rows;
 };
 
 template <int BN, int STAGES, int EPI>
@@ -51,8 +56,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // shared-memory base rounded up to the 1024 bytes the swizzle pattern needs
     const unsigned smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const int m0 = blockIdx.y * kTileM;
+    int m0 = blockIdx.y * kTileM;
     const int n0 = blockIdx.x * (EPI == kTcSwiGlu ? BN / 2 : BN);
+    int b_row0 = n0, rows_here = p.m - m0;
+    if (p.table != nullptr) {
+        if ((int)blockIdx.y >= p.table[0]) return;          // (the whole block, before anything is set up)
+        const int* entry = p.table + 4 + 3 * blockIdx.y;
+        b_row0 = entry[0] * p.group_rows + n0;
+        m0 = entry[1];
+        rows_here = entry[2];
+    }
     const int k_tiles = (p.k + kTileK - 1) / kTileK;
 
     if (threadIdx.x == 0) {
@@ -87,7 +100,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 tma_load_2d(b_dst, &map_b, bar, kt * kTileK, n0);                      // gate rows
                 tma_load_2d(b_dst + kBytesB / 2, &map_b, bar, kt * kTileK, p.n + n0);  // their up rows
             } else {
-                tma_load_2d(b_dst, &map_b, bar, kt * kTileK, n0);
+                tma_load_2d(b_dst, &map_b, bar, kt * kTileK, b_row0);
             }
         }
     } else if (warp == 1 && lane == 0) {
@@ -122,6 +135,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tcgen05_fence_after();
     if (have_accumulator) {
         const int row = m0 + warp * 32 + lane;
+        const bool row_ok = warp * 32 + lane < rows_here;
         constexpr int kOutColumns = EPI == kTcSwiGlu ? BN / 2 : BN;
 #pragma unroll 1
         for (int c0 = 0; c0 < kOutColumns; c0 += 32) {
@@ -143,7 +157,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int i = 0; i < 32; ++i)        // the product as a plain product would store it, then the activation
                     v[i] = activate(__bfloat162float(__float2bfloat16_rn(v[i])), p.activation);
             }
-            if (row < p.m) {
+            if (row_ok) {
                 const int col = n0 + c0;
                 if (EPI == kTcStoreF32) {
                     float* dst = reinterpret_cast<float*>(p.c) + (size_t)row * p.ldc + col;
@@ -521,7 +535,7 @@ CELEG_API int celeg_gemm_tcgen05(const void* a, int lda, const void* b, int ldb,
     if (!tensor_map_for(a, m, k, lda, kTileM, &map_a)) return -3;
     const long long b_rows = epilogue == kTcSwiGlu ? 2ll * n : n;
     if (!tensor_map_for(b, b_rows, k, ldb, epilogue == kTcSwiGlu ? bn / 2 : bn, &map_b)) return -3;
-    TcGemmParams p{m, n, k, c, ldc, error_flag, epilogue >= kTcActivation ? epilogue - kTcActivation : 0};
+    TcGemmParams p{m, n, k, c, ldc, error_flag, epilogue >= kTcActivation ? epilogue - kTcActivation : 0, nullptr, 0};
     if (epilogue > kTcActivation) epilogue = kTcActivation;
 #define CELEG_TC_DISPATCH(BN, STAGES)                                                        \
     switch (epilogue) {                                                                      \
@@ -554,4 +568,45 @@ CELEG_API int celeg_gemm_tcgen05(const void* a, int lda, const void* b, int ldb,
     }
     CELEG_TC_DISPATCH(128, 3)          // two blocks per SM: one's epilogue under the other's main loop
 #undef CELEG_TC_DISPATCH
+}
+
+// Grouped product: c[r, :n] = a[r, :k] * b[g(r)][:n, :k]^T, where b holds `groups` matrices of n rows one after the
+// other and the device-made table (see TcGemmParams) assigns runs of rows of a to groups in tiles of at most 128
+// rows. max_tiles bounds the table's tiles and sizes the grid; rows of a: a_rows. epilogue 0 (bfloat16) or 3.. (an
+// activation). The same kernel as the plain product with 128 x 128 tiles, two blocks per SM.
+CELEG_API int celeg_gemm_tcgen05_grouped(const void* a, int lda, int a_rows, const void* b, int ldb, int groups, void* c,
+                                         int ldc, const int* table, int max_tiles, int n, int k, int epilogue,
+                                         int* error_flag, cudaStream_t stream) {
+    CELEG_REQUIRE(a_rows > 0 && n > 0 && k > 0 && groups > 0 && max_tiles >= 0 && table != nullptr,
+                  "gemm_tcgen05_grouped: invalid sizes rows=%d n=%d k=%d groups=%d tiles=%d", a_rows, n, k, groups, max_tiles);
+    CELEG_REQUIRE(k % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && lda >= k && ldb >= k,
+                  "gemm_tcgen05_grouped: k=%d, lda=%d and ldb=%d must be multiples of 8 and cover k", k, lda, ldb);
+    CELEG_REQUIRE((((size_t)a | (size_t)b) & 15) == 0, "gemm_tcgen05_grouped: operands must be 16-byte aligned");
+    CELEG_REQUIRE(ldc >= n && error_flag != nullptr, "gemm_tcgen05_grouped: ldc=%d is smaller than n=%d, or no error flag", ldc, n);
+    CELEG_REQUIRE(epilogue == kTcStoreBf16 || (epilogue >= kTcActivation && epilogue <= 6),
+                  "gemm_tcgen05_grouped: unknown epilogue %d", epilogue);
+    CELEG_REQUIRE(max_tiles <= 65535, "gemm_tcgen05_grouped: %d tiles exceed one launch", max_tiles);
+    if (max_tiles == 0) return 0;
+    CUtensorMap map_a, map_b;
+    if (!tensor_map_for(a, a_rows, k, lda, kTileM, &map_a)) return -3;
+    if (!tensor_map_for(b, (long long)groups * n, k, ldb, 128, &map_b)) return -3;
+    TcGemmParams p{a_rows, n, k, c, ldc, error_flag, epilogue >= kTcActivation ? epilogue - kTcActivation : 0, table, n};
+    constexpr int BN = 128, STAGES = 3;
+    constexpr size_t smem = (size_t)STAGES * (kTileM * kTileK * 2 + BN * kTileK * 2) + 1024;
+    dim3 grid((n + BN - 1) / BN, max_tiles);
+    cudaError_t status;
+    if (epilogue == kTcStoreBf16) {
+        auto kernel = gemm_tcgen05_kernel<BN, STAGES, kTcStoreBf16>;
+        status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (status == cudaSuccess) kernel<<<grid, kGemmThreads, smem, stream>>>(map_a, map_b, p);
+    } else {
+        auto kernel = gemm_tcgen05_kernel<BN, STAGES, kTcActivation>;
+        status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (status == cudaSuccess) kernel<<<grid, kGemmThreads, smem, stream>>>(map_a, map_b, p);
+    }
+    if (status != cudaSuccess) {
+        set_error("gemm_tcgen05_grouped: %s", cudaGetErrorString(status));
+        return -2;
+    }
+    return check_launch("gemm_tcgen05_grouped");
 }

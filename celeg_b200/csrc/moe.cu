@@ -100,7 +100,8 @@ __global__ void moe_route_kernel(const A* h, int h_stride, const float* router, 
 // ------------------------------------------------------------------------------------------------ grouping
 // layout of `table` (int32): [0] number of tiles; then per tile (expert, first place, rows) from table[4] on
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int* chosen, int pairs, int experts, int top,
-                                                         int* place_of_pair, int* source_of_place, int* table) {
+                                                         int tile_rows, int* place_of_pair, int* source_of_place,
+                                                         int* table) {
     extern __shared__ int group_smem[];            // counts [experts] | cursor [experts]
     chain_release();
     chain_wait();
@@ -114,10 +115,10 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* chosen, int 
         int at = 0, tiles = 0;
         for (int e = 0; e < experts; ++e) {
             cursor[e] = at;
-            for (int first = 0; first < counts[e]; first += kMoeTile) {
+            for (int first = 0; first < counts[e]; first += tile_rows) {
                 table[4 + 3 * tiles] = e;
                 table[4 + 3 * tiles + 1] = at + first;
-                table[4 + 3 * tiles + 2] = min(kMoeTile, counts[e] - first);
+                table[4 + 3 * tiles + 2] = min(tile_rows, counts[e] - first);
                 ++tiles;
             }
             at += counts[e];
@@ -129,6 +130,21 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* chosen, int 
         const int place = atomicAdd(&cursor[chosen[p]], 1);
         place_of_pair[p] = place;
         source_of_place[place] = p / top;
+    }
+}
+
+// one block a place: a row copied in units of 16 bytes (or of one element, where rows are not aligned)
+__global__ void moe_gather_rows_kernel(const unsigned char* x, long long x_stride_bytes, const int* source,
+                                       unsigned char* out, long long out_stride_bytes, int bytes, int unit) {
+    chain_release();
+    chain_wait();
+    const unsigned char* src = x + (long long)source[blockIdx.x] * x_stride_bytes;
+    unsigned char* dst = out + (long long)blockIdx.x * out_stride_bytes;
+    if (unit == 16) {
+        for (int i = threadIdx.x * 16; i < bytes; i += blockDim.x * 16)
+            *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+    } else {
+        for (int i = threadIdx.x; i < bytes; i += blockDim.x) dst[i] = src[i];
     }
 }
 
@@ -332,15 +348,32 @@ CELEG_API int celeg_moe_route(const void* h, int h_stride, const float* router, 
     return check_launch("moe_route");
 }
 
-// table: int32 [4 + 3 * (pairs / 64 + experts)] at least
-CELEG_API int celeg_moe_group(const int* chosen, int tokens, int experts, int top, int* place_of_pair,
+// table: int32 [4 + 3 * (pairs / tile_rows + experts)] at least; tile_rows: 64 for this file's products, 128 for the
+// grouped tcgen05 product
+CELEG_API int celeg_moe_group(const int* chosen, int tokens, int experts, int top, int tile_rows, int* place_of_pair,
                               int* source_of_place, int* table, cudaStream_t stream) {
-    CELEG_REQUIRE(tokens >= 0 && experts > 0 && top > 0 && experts <= 4096,
-                  "moe_group: invalid sizes tokens=%d experts=%d top=%d", tokens, experts, top);
+    CELEG_REQUIRE(tokens >= 0 && experts > 0 && top > 0 && experts <= 4096 && (tile_rows == kMoeTile || tile_rows == 128),
+                  "moe_group: invalid sizes tokens=%d experts=%d top=%d tile_rows=%d", tokens, experts, top, tile_rows);
     if (tokens == 0) return 0;
     launch_chained(moe_group_kernel, 1, 1024, (size_t)2 * experts * sizeof(int), stream, chosen, tokens * top, experts,
-                   top, place_of_pair, source_of_place, table);
+                   top, tile_rows, place_of_pair, source_of_place, table);
     return check_launch("moe_group");
+}
+
+// out[place] = x[source[place]] for every place: the rows of a step ordered by expert, for a product that reads
+// its operand by TMA
+CELEG_API int celeg_moe_gather_rows(const void* x, int x_stride, const int* source, void* out, int out_stride, int places,
+                                    int width, int act_dtype, cudaStream_t stream) {
+    CELEG_REQUIRE(places >= 0 && width > 0, "moe_gather_rows: invalid sizes places=%d width=%d", places, width);
+    CELEG_REQUIRE(act_dtype == kFloat32 || act_dtype == kBFloat16, "moe_gather_rows: unknown dtype code %d", act_dtype);
+    if (places == 0) return 0;
+    const int bytes = width * (act_dtype == kFloat32 ? 4 : 2);
+    const int unit = (bytes % 16 == 0 && ((size_t)x & 15) == 0 && ((size_t)out & 15) == 0 &&
+                      (x_stride * (bytes / width)) % 16 == 0 && (out_stride * (bytes / width)) % 16 == 0) ? 16 : (bytes / width);
+    launch_chained(moe_gather_rows_kernel, places, 128, 0, stream, (const unsigned char*)x,
+                   (long long)x_stride * (bytes / width), source, (unsigned char*)out, (long long)out_stride * (bytes / width),
+                   bytes, unit);
+    return check_launch("moe_gather_rows");
 }
 
 // out[place, :n] = act(x[source[place]] . W[expert of the place's tile]^T); max_tiles bounds the table's tiles

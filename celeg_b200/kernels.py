@@ -113,7 +113,10 @@ _SIGNATURES = {
     "celeg_head_gate": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_moe_route": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                         c_int, c_int, c_void_p],
-    "celeg_moe_group": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "celeg_moe_group": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "celeg_moe_gather_rows": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "celeg_gemm_tcgen05_grouped": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+                                   c_int, c_int, c_void_p, c_void_p],
     "celeg_expert_product": [c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_int,
                              c_int, c_int, c_int, c_int, c_void_p],
     "celeg_expert_rows": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int,
@@ -728,9 +731,9 @@ def head_gate(values: torch.Tensor, head_width: int, gate: torch.Tensor, tokens:
 MOE_TILE = 64
 
 
-def moe_max_tiles(pairs: int, experts: int) -> int:
+def moe_max_tiles(pairs: int, experts: int, tile_rows: int = MOE_TILE) -> int:
     """The most row tiles that ``pairs`` (token, choice) pairs can make, however they fall on the experts."""
-    return pairs // MOE_TILE + min(pairs, experts)
+    return pairs // tile_rows + min(pairs, experts)
 
 
 def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor],
@@ -748,12 +751,39 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.
 
 
 def moe_group(chosen: torch.Tensor, tokens: int, experts: int, top: int, place_of_pair: torch.Tensor,
-              source_of_place: torch.Tensor, table: torch.Tensor) -> None:
+              source_of_place: torch.Tensor, table: torch.Tensor, tile_rows: int = MOE_TILE) -> None:
     """Orders the (token, choice) pairs by expert: place_of_pair [tokens * top], source_of_place [tokens * top] (the
-    token of each place) and the tile table int32 [4 + 3 * moe_max_tiles] (count, then (expert, first place, rows))."""
-    assert table.numel() >= 4 + 3 * moe_max_tiles(tokens * top, experts)
-    _check(library().celeg_moe_group(_ptr(chosen), tokens, experts, top, _ptr(place_of_pair), _ptr(source_of_place),
-                                     _ptr(table), _stream()))
+    token of each place) and the tile table int32 [4 + 3 * moe_max_tiles] (count, then (expert, first place, rows) for
+    runs of at most ``tile_rows`` places of one expert)."""
+    assert table.numel() >= 4 + 3 * moe_max_tiles(tokens * top, experts, tile_rows)
+    _check(library().celeg_moe_group(_ptr(chosen), tokens, experts, top, tile_rows, _ptr(place_of_pair),
+                                     _ptr(source_of_place), _ptr(table), _stream()))
+
+
+def moe_gather_rows(x: torch.Tensor, source: torch.Tensor, out: torch.Tensor, places: int) -> None:
+    """out[place] = x[source[place]]: the step's rows in the order of the experts that chose them."""
+    assert x.dtype == out.dtype and x.stride(-1) == 1 and out.stride(-1) == 1 and x.shape[-1] == out.shape[-1]
+    _check(library().celeg_moe_gather_rows(_ptr(x), x.stride(0), _ptr(source), _ptr(out), out.stride(0), places,
+                                           x.shape[-1], dtype_code(x.dtype), _stream()))
+
+
+def expert_product_tcgen05_supported(x: torch.Tensor, weights: torch.Tensor) -> bool:
+    """Shapes the grouped tcgen05 product takes: bfloat16, k and the row strides multiples of 8, 16-byte aligned."""
+    return (x.dtype == torch.bfloat16 and weights.dtype == torch.bfloat16 and weights.is_contiguous()
+            and weights.shape[2] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(-1) == 1
+            and x.data_ptr() % 16 == 0 and weights.data_ptr() % 16 == 0)
+
+
+def expert_product_tcgen05(x: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, table: torch.Tensor,
+                           max_tiles: int, activation: int, error_flag: torch.Tensor) -> None:
+    """out[place] = act(x[place] @ weights[expert of the place]^T) on tcgen05 over a tile table of 128-row tiles;
+    ``x`` holds the rows in the order of their places. ``activation``: a code of ACT_* or -1."""
+    _, n, k = weights.shape
+    assert out.dtype == torch.bfloat16 and out.stride(-1) == 1 and out.shape[-1] == n and x.shape[-1] == k
+    _check(library().celeg_gemm_tcgen05_grouped(_ptr(x), x.stride(0), x.shape[0], _ptr(weights), weights.stride(1),
+                                                weights.shape[0], _ptr(out), out.stride(0), _ptr(table), max_tiles, n, k,
+                                                TC_STORE if activation < 0 else TC_ACTIVATION + activation,
+                                                _ptr(error_flag), _stream()))
 
 
 def expert_product(x: torch.Tensor, source: Optional[torch.Tensor], weights: torch.Tensor, out: torch.Tensor,

@@ -79,7 +79,10 @@ class MoeFeedForward:
 
     Steps of few tokens stream the chosen experts' matrices once per (token, choice) pair; larger steps order the
     pairs by expert on the device and run both products tile by tile over a table the device makes, on a grid
-    sized for the worst case, so that nothing on the host depends on the routing (kernels: csrc/moe.cu)."""
+    sized for the worst case, so that nothing on the host depends on the routing (kernels: csrc/moe.cu). On the
+    bfloat16 path those two products are the grouped form of the tcgen05 product (csrc/gemm_tcgen05.cu: TMA boxes
+    of 128 rows out of the rows gathered in expert order and out of the experts' stacked matrices, the activation
+    in the epilogue), where the shapes allow it."""
 
     FEW_TOKENS = 16
 
@@ -109,6 +112,7 @@ class MoeFeedForward:
         self.place = rt.flat_scratch("moe.place", pairs, torch.int32)
         self.source = rt.flat_scratch("moe.source", pairs, torch.int32)
         self.table = rt.flat_scratch("moe.table", 4 + 3 * kernels.moe_max_tiles(pairs, self.experts), torch.int32, zero=True)
+        self.gathered = rt.flat_scratch("moe.gathered", pairs * self.hidden, rt.act_dtype).view(pairs, self.hidden)
         self.raised = rt.flat_scratch("moe.raised", pairs * self.inner, rt.act_dtype).view(pairs, self.inner)
         self.lowered = rt.flat_scratch("moe.lowered", pairs * self.hidden, rt.act_dtype).view(pairs, self.hidden)
         self.shared_out = rt.scratch("moe.shared_out", self.hidden) if self.shared is not None else None
@@ -125,6 +129,15 @@ class MoeFeedForward:
             kernels.expert_rows(x, top, self.chosen, self.w_up, self.raised, pairs, self.activation)
             kernels.expert_rows(self.raised, 1, self.chosen, self.w_down, self.lowered, pairs, -1)
             place = None
+        elif (self.rt.tensor_core_products != "none" and kernels.expert_product_tcgen05_supported(self.gathered, self.w_up)
+              and kernels.expert_product_tcgen05_supported(self.raised, self.w_down)):
+            kernels.moe_group(self.chosen, t, self.experts, top, self.place, self.source, self.table, tile_rows=128)
+            tiles = kernels.moe_max_tiles(pairs, self.experts, 128)
+            kernels.moe_gather_rows(x, self.source, self.gathered, pairs)
+            kernels.expert_product_tcgen05(self.gathered, self.w_up, self.raised, self.table, tiles, self.activation,
+                                           self.rt.error_flag)
+            kernels.expert_product_tcgen05(self.raised, self.w_down, self.lowered, self.table, tiles, -1, self.rt.error_flag)
+            place = self.place
         else:
             kernels.moe_group(self.chosen, t, self.experts, top, self.place, self.source, self.table)
             tiles = kernels.moe_max_tiles(pairs, self.experts)

@@ -271,9 +271,10 @@ def test_router_chooses_by_corrected_scores(dtype, experts, top, width, tokens):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("experts,top,width,inner,tokens", [(4, 2, 40, 24, 7), (16, 3, 256, 64, 200), (5, 5, 36, 20, 70),
-                                                             (40, 1, 64, 72, 130), (3, 2, 100, 33, 90)])
+                                                             (40, 1, 64, 72, 130), (3, 2, 100, 33, 90), (8, 2, 512, 384, 700)])
 def test_experts_products_grouped_and_row_by_row(dtype, experts, top, width, inner, tokens):
-    """Both forms of the experts' two products against the plain mixture, and against each other."""
+    """The forms of the experts' two products (tile by tile over the pairs grouped by expert, on tcgen05 where the
+    shapes allow, and row by row) against the plain mixture, and against each other."""
     from celeg_b200 import kernels
     rng = np.random.default_rng(7)
     h = rounded(rng.normal(size=(tokens, width)), dtype)
@@ -297,24 +298,41 @@ def test_experts_products_grouped_and_row_by_row(dtype, experts, top, width, inn
     chosen, weights = dev(chosen_np.reshape(-1)), dev(weights_np.reshape(-1))
     x, w_up, w_down = dev(h, dtype), dev(up, dtype), dev(down, dtype)
     results = []
-    for grouped in (True, False):
-        if not grouped and pairs > 1000:
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for form in ("grouped", "tcgen05", "rows"):
+        if form == "rows" and pairs > 1000:
             continue
-        raised = torch.zeros((pairs, inner), dtype=dtype, device="cuda")
-        lowered = torch.zeros((pairs, width), dtype=dtype, device="cuda")
+        # (spare rows after the step's pairs, full of what an earlier step left: no tile may take them for its own)
+        raised = torch.full((pairs + 200, inner), 3.0, dtype=dtype, device="cuda")
+        lowered = torch.full((pairs + 200, width), 3.0, dtype=dtype, device="cuda")
         y = torch.zeros((tokens, width), dtype=dtype, device="cuda")
-        if grouped:
+        if form == "tcgen05":
+            gathered = torch.full((pairs + 200, width), 3.0, dtype=dtype, device="cuda")
+            if not (kernels.expert_product_tcgen05_supported(gathered, w_up) and kernels.expert_product_tcgen05_supported(raised, w_down)):
+                continue
+        if form != "rows":
+            tile_rows = 128 if form == "tcgen05" else kernels.MOE_TILE
             place = torch.zeros(pairs, dtype=torch.int32, device="cuda")
             source = torch.zeros(pairs, dtype=torch.int32, device="cuda")
-            tiles = kernels.moe_max_tiles(pairs, experts)
+            tiles = kernels.moe_max_tiles(pairs, experts, tile_rows)
             table = torch.zeros(4 + 3 * tiles, dtype=torch.int32, device="cuda")
-            kernels.moe_group(chosen, tokens, experts, top, place, source, table)
+            kernels.moe_group(chosen, tokens, experts, top, place, source, table, tile_rows=tile_rows)
             places = place.cpu().numpy()
             assert sorted(places.tolist()) == list(range(pairs))
             assert np.array_equal(source.cpu().numpy()[places], np.arange(pairs) // top)
             assert np.all(np.diff(chosen_np.reshape(-1)[np.argsort(places)]) >= 0)         # places are ordered by expert
-            kernels.expert_product(x, source, w_up, raised, table, tiles, kernels.ACT_RELU_SQUARED)
-            kernels.expert_product(raised, None, w_down, lowered, table, tiles, -1)
+            listed = table.cpu().numpy()
+            assert listed[0] <= tiles and listed[4 + 2:4 + 3 * listed[0]:3].sum() == pairs
+            if form == "tcgen05":
+                kernels.moe_gather_rows(x, source, gathered, pairs)
+                assert torch.equal(gathered[:pairs], x[source.long()])
+                kernels.expert_product_tcgen05(gathered, w_up, raised, table, tiles, kernels.ACT_RELU_SQUARED, flag)
+                kernels.expert_product_tcgen05(raised, w_down, lowered, table, tiles, -1, flag)
+                assert int(flag.item()) == 0
+            else:
+                kernels.expert_product(x, source, w_up, raised, table, tiles, kernels.ACT_RELU_SQUARED)
+                kernels.expert_product(raised, None, w_down, lowered, table, tiles, -1)
+            assert torch.all(raised[pairs:] == 3.0) and torch.all(lowered[pairs:] == 3.0)
             kernels.moe_combine(lowered, place, weights, dev(shared_np, dtype), dev(gate_np), y, tokens, top)
         else:
             kernels.expert_rows(x, top, chosen, w_up, raised, pairs, kernels.ACT_RELU_SQUARED)
@@ -322,5 +340,5 @@ def test_experts_products_grouped_and_row_by_row(dtype, experts, top, width, inn
             kernels.moe_combine(lowered, None, weights, dev(shared_np, dtype), dev(gate_np), y, tokens, top)
         close(y, want, dtype, scale=np.abs(want).max())
         results.append(y)
-    if len(results) == 2 and dtype == torch.float32:
-        assert (results[0] - results[1]).abs().max() <= 1e-5 * results[0].abs().max()
+    if len(results) >= 2 and dtype == torch.float32:
+        assert (results[0] - results[-1]).abs().max() <= 1e-5 * results[0].abs().max()
