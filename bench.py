@@ -8,7 +8,7 @@ batch 1 and 64. Prints ONE JSON line.
                   [--prefill-tokens T] [--chunk C] [--kernel-times] [--no-cuda-graph]      one phase, a short record
   python bench.py --workload lfm2-700m|lfm2-350m [--requests N] [--new-tokens N] [--max-batched-tokens N]
                   [--prefill-chunk N] [--kernel-times]       a scheduler workload through Engine.submit/step/poll
-  python bench.py --design ramosun [--design-size w1024|w2048] [--kernel-times]
+  python bench.py --design ramosun|kedesun [--design-size w1024|w2048] [--kernel-times]
                   the Ramosun design beside the closest LFM2 model at equal size: prefill of 2,048 tokens, decode at batch 8
 
 A "step" is one decode step of the whole batch. ``value`` is timed on the device (CUDA events
@@ -194,7 +194,9 @@ class KernelTimer:
              "attention_decode_fused", "attention_prefill", "attention_prefill_tcgen05", "gemv_bf16", "gemm_tcgen05",
              "gemm_stream", "gemm_f32", "swiglu", "sample", "sample_greedy", "mark_seen",
              "add_dyt", "add_to_residual", "join_stream_embedding", "activation", "softcap", "recurrent_scan",
-             "mlstm_gates", "delta_prepare", "gated_head_norm", "qk_whole_norm_rope_store", "recurrent_decode")
+             "mlstm_gates", "delta_prepare", "gated_head_norm", "qk_whole_norm_rope_store", "recurrent_decode",
+             "depth_average", "latent_prepare", "head_project", "head_gate", "moe_route", "moe_group", "moe_gather_rows",
+             "expert_product", "expert_product_tcgen05", "expert_rows", "moe_combine")
 
     def __init__(self):
         self.pairs = []
@@ -223,12 +225,15 @@ class KernelTimer:
                 setattr(kernels, name, self._wrap(name, self.saved[name]))
         self.saved["torch.mm"] = torch.mm
         torch.mm = self._wrap("library product (torch.mm)", torch.mm)
+        self.saved["torch.bmm"] = torch.bmm
+        torch.bmm = self._wrap("batched library product (torch.bmm)", torch.bmm)
         return self
 
     def __exit__(self, *exc):
         import torch
         from celeg_b200 import kernels
         torch.mm = self.saved.pop("torch.mm")
+        torch.bmm = self.saved.pop("torch.bmm")
         for name, function in self.saved.items():
             setattr(kernels, name, function)
         self.saved = {}
@@ -474,6 +479,24 @@ def ramosun_config(width: int, vocab: int) -> dict:
             "max_context": 8192}
 
 
+def kedesun_config(width: int, vocab: int) -> dict:
+    """Eight blocks: retention, retention with experts, latent attention, retention with experts, twice. Heads of 64
+    (keys) and 128 (values) in the retention; sixteenth-of-the-width many attention heads of 64 + 64 over a cached
+    vector of 192 + 64; a SwiGLU of 8/3 width, or 32 experts of half the width of which a token uses 4, beside a
+    shared expert of the width (6 width^2 active parameters against the SwiGLU's 8)."""
+    heads = width // 128
+    dense = {"kind": "dense", "ff": (8 * width // 3 + 127) // 128 * 128}
+    experts = {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": width // 2}, "shared": {"ff": width}}
+    decay = [1.0 - 2.0 ** (-5.0 - 7.0 * head / max(heads - 1, 1)) for head in range(heads)]
+    retention = {"type": "retention", "mixer": {"heads": heads, "dim": 64, "vdim": 128, "decay": decay}}
+    latent = {"type": "latent_attention", "mixer": {
+        "heads": heads, "dim": 64, "rot_dim": 64, "vdim": 64, "kv_rank": 192, "scale": 128 ** -0.5,
+        "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    run = [dict(retention, mlp=dense), dict(retention, mlp=experts), dict(latent, mlp=dense), dict(retention, mlp=experts)]
+    return {"architecture": "Kedesun", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": run + run,
+            "max_context": 8192}
+
+
 def lfm2_relative(width: int, vocab: int) -> dict:
     raw = dict(LFM2_1P2B)
     # eight blocks like Ramosun's run order; a SwiGLU of 8/3 width has the parameters of a dense feed-forward of 4 width
@@ -496,7 +519,12 @@ def run_design(args) -> dict:
         if args.design_size and tag != args.design_size:
             continue
         entry = {}
-        for name, raw in (("ramosun", ramosun_config(width, vocab)), ("lfm2", lfm2_relative(width, vocab))):
+        if args.design == "kedesun":     # beside both earlier designs: Ramosun has its block form and matrix states
+            models = (("kedesun", kedesun_config(width, vocab)), ("ramosun", ramosun_config(width, vocab)),
+                      ("lfm2", lfm2_relative(width, vocab)))
+        else:
+            models = (("ramosun", ramosun_config(width, vocab)), ("lfm2", lfm2_relative(width, vocab)))
+        for name, raw in models:
             folder = model_folder(raw)
             options = EngineOptions(max_active_requests=8, max_batched_tokens=PREFILL_TOKENS,
                                     prefill_chunk_tokens=PREFILL_TOKENS, page_tokens=args.page_tokens,
@@ -775,7 +803,7 @@ def main() -> int:
     parser.add_argument("--new-tokens", type=int, default=0, help="--workload: tokens to generate per request")
     parser.add_argument("--max-batched-tokens", type=int, default=0, help="--workload: token budget of a step")
     parser.add_argument("--prefill-chunk", type=int, default=0, help="--workload: longest prompt portion")
-    parser.add_argument("--design", default=None, choices=["ramosun"],
+    parser.add_argument("--design", default=None, choices=["ramosun", "kedesun"],
                         help="prefill and decode of that design beside the closest LFM2 model at equal size")
     parser.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES), help="--design: one size only")
     parser.add_argument("--no-warmup-run", action="store_true",

@@ -1,9 +1,10 @@
 // Mixture of experts: router, grouping of (token, choice) pairs by expert, the experts' two products, and the
 // weighted sum.
 //
-//   route      z = W_r h (float32 sums); s = softmax(z) over all experts; the `top` experts with the largest
-//              s + correction are chosen (ties: the lower index), their weights are s / (sum of the chosen s + 1e-20);
-//              also sigmoid(w_sg . h), the gate of a shared expert. One warp a token.
+//   route      from z = W_r h (a product with float32 sums, made before): s = softmax(z) over all experts; the `top`
+//              experts with the largest s + correction are chosen (ties: the lower index), their weights are
+//              s / (sum of the chosen s + 1e-20); also the sigmoid of one more column of z, the gate of a shared
+//              expert. One warp a token.
 //   group      pairs (token, choice) ordered by expert: the source row of every place, the place of every pair,
 //              and a table of row tiles (expert, first place, rows) for the products. One block, one launch;
 //              the order inside an expert is not fixed, and no result depends on it.
@@ -29,10 +30,10 @@ __device__ __forceinline__ float expert_activation(float z, int kind) {
 }
 
 // ------------------------------------------------------------------------------------------------ router
-template <typename A>
-__global__ void moe_route_kernel(const A* h, int h_stride, const float* router, const float* correction,
-                                 const float* shared_gate_w, int* chosen, float* weights, float* shared_gate,
-                                 int tokens, int width, int experts, int top) {
+// logits: float32 [tokens, stride] = h W_r^T from a product with float32 sums (column `experts`, if asked for, is the
+// shared expert's gate before its sigmoid). One warp a token: softmax over all experts, the choice, the weights.
+__global__ void moe_route_kernel(const float* logits, int stride, const float* correction, int gate_column,
+                                 int* chosen, float* weights, float* shared_gate, int tokens, int experts, int top) {
     extern __shared__ float route_smem[];          // per warp: scores [experts]
     chain_release();
     chain_wait();
@@ -40,32 +41,23 @@ __global__ void moe_route_kernel(const A* h, int h_stride, const float* router, 
     const int t = blockIdx.x * warps + warp;
     if (t >= tokens) return;
     float* scores = route_smem + (size_t)warp * experts;
-    const A* row = h + (size_t)t * h_stride;
-    for (int e = 0; e < experts; ++e) {
-        const float* w = router + (size_t)e * width;
-        float sum = 0.0f;
-        for (int c = lane; c < width; c += 32) sum = fmaf(to_float(row[c]), w[c], sum);
-        sum = warp_sum(sum);
-        if (lane == 0) scores[e] = sum;
-    }
-    if (shared_gate_w) {
-        float sum = 0.0f;
-        for (int c = lane; c < width; c += 32) sum = fmaf(to_float(row[c]), shared_gate_w[c], sum);
-        sum = warp_sum(sum);
-        if (lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-sum));
-    }
-    __syncwarp();
+    const float* row = logits + (size_t)t * stride;
+    if (gate_column >= 0 && lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-row[gate_column]));
     float largest = -INFINITY;
-    for (int e = lane; e < experts; e += 32) largest = fmaxf(largest, scores[e]);
+    for (int e = lane; e < experts; e += 32) largest = fmaxf(largest, row[e]);
     largest = warp_max(largest);
     float total = 0.0f;
-    for (int e = lane; e < experts; e += 32) total += expf(scores[e] - largest);
+    for (int e = lane; e < experts; e += 32) {
+        const float p = expf(row[e] - largest);
+        scores[e] = p;
+        total += p;
+    }
     total = warp_sum(total);
     __syncwarp();
-    for (int e = lane; e < experts; e += 32) scores[e] = expf(scores[e] - largest) / total;
+    for (int e = lane; e < experts; e += 32) scores[e] = scores[e] / total;
     __syncwarp();
     // the `top` largest of s + correction, one after the other; a taken expert is marked by a negative score
-    // (scores are positive), its value kept in a register of lane 0
+    // (scores are not negative)
     float picked_sum = 0.0f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
@@ -288,7 +280,7 @@ __global__ void __launch_bounds__(128) expert_product_mma_kernel(const ExpertPro
 template <typename A>
 __global__ void expert_rows_kernel(const A* x, int x_stride, int pairs_per_row, const int* chosen, const A* weights,
                                    long long expert_stride, int w_stride, A* out, int out_stride, int pairs, int n, int k,
-                                   int activation) {
+                                   int activation, int vectors) {
     chain_release();
     chain_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
@@ -298,7 +290,34 @@ __global__ void expert_rows_kernel(const A* x, int x_stride, int pairs_per_row, 
     const A* row = x + (size_t)(pair / pairs_per_row) * x_stride;
     const A* w = weights + (size_t)chosen[pair] * expert_stride + (size_t)j * w_stride;
     float sum = 0.0f;
-    for (int c = lane; c < k; c += 32) sum = fmaf(to_float(row[c]), to_float(w[c]), sum);
+    if (sizeof(A) == 2 && vectors) {
+        // 8 elements a load, four loads of the weights in flight a lane
+        const uint4* rv = reinterpret_cast<const uint4*>(row);
+        const uint4* wv = reinterpret_cast<const uint4*>(w);
+        const int pieces = k >> 3;
+        float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int c0 = lane; c0 < pieces; c0 += 128) {
+            uint4 wq[4], xq[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (c0 + 32 * u < pieces) { wq[u] = __ldg(wv + c0 + 32 * u); xq[u] = rv[c0 + 32 * u]; }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (c0 + 32 * u >= pieces) continue;
+                const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wq[u]);
+                const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xq[u]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 a = __bfloat1622float2(xh[i]), b = __bfloat1622float2(wh[i]);
+                    part[u] = fmaf(a.x, b.x, part[u]);
+                    part[u] = fmaf(a.y, b.y, part[u]);
+                }
+            }
+        }
+        sum = (part[0] + part[1]) + (part[2] + part[3]);
+    } else {
+        for (int c = lane; c < k; c += 32) sum = fmaf(to_float(row[c]), to_float(w[c]), sum);
+    }
     sum = warp_sum(sum);
     if (lane == 0) out[(size_t)pair * out_stride + j] = from_float<A>(expert_activation(sum, activation));
 }
@@ -326,25 +345,19 @@ __global__ void moe_combine_kernel(const A* expert_out, int out_stride, const in
 
 using namespace celeg_b200;
 
-CELEG_API int celeg_moe_route(const void* h, int h_stride, const float* router, const float* correction,
-                              const float* shared_gate_w, int* chosen, float* weights, float* shared_gate, int tokens,
-                              int width, int experts, int top, int act_dtype, cudaStream_t stream) {
-    CELEG_REQUIRE(tokens >= 0 && width > 0 && experts > 0 && top > 0 && top <= experts,
-                  "moe_route: invalid sizes tokens=%d width=%d experts=%d top=%d", tokens, width, experts, top);
+CELEG_API int celeg_moe_route(const float* logits, int stride, const float* correction, int gate_column, int* chosen,
+                              float* weights, float* shared_gate, int tokens, int experts, int top, cudaStream_t stream) {
+    CELEG_REQUIRE(tokens >= 0 && experts > 0 && top > 0 && top <= experts && stride >= experts,
+                  "moe_route: invalid sizes tokens=%d experts=%d top=%d stride=%d", tokens, experts, top, stride);
     CELEG_REQUIRE(experts <= 2048, "moe_route: %d experts exceed a block's shared memory", experts);
-    CELEG_REQUIRE(act_dtype == kFloat32 || act_dtype == kBFloat16, "moe_route: unknown dtype code %d", act_dtype);
-    CELEG_REQUIRE(shared_gate_w == nullptr || shared_gate != nullptr, "moe_route: a shared gate needs its output");
+    CELEG_REQUIRE(gate_column < stride && (gate_column < 0 || shared_gate != nullptr),
+                  "moe_route: the shared gate's column %d lies outside a row of %d, or has no output", gate_column, stride);
     if (tokens == 0) return 0;
     const int warps = 4;
     const size_t smem = (size_t)warps * experts * sizeof(float);
     const unsigned blocks = (unsigned)((tokens + warps - 1) / warps);
-    if (act_dtype == kFloat32)
-        launch_chained(moe_route_kernel<float>, blocks, warps * 32, smem, stream, (const float*)h, h_stride, router,
-                       correction, shared_gate_w, chosen, weights, shared_gate, tokens, width, experts, top);
-    else
-        launch_chained(moe_route_kernel<__nv_bfloat16>, blocks, warps * 32, smem, stream, (const __nv_bfloat16*)h,
-                       h_stride, router, correction, shared_gate_w, chosen, weights, shared_gate, tokens, width, experts,
-                       top);
+    launch_chained(moe_route_kernel, blocks, warps * 32, smem, stream, logits, stride, correction, gate_column, chosen,
+                   weights, shared_gate, tokens, experts, top);
     return check_launch("moe_route");
 }
 
@@ -409,14 +422,16 @@ CELEG_API int celeg_expert_rows(const void* x, int x_stride, int pairs_per_row, 
     if (pairs == 0) return 0;
     const int warps = 8;
     dim3 grid((n + warps - 1) / warps, pairs);
+    const int vectors = k % 8 == 0 && x_stride % 8 == 0 && w_stride % 8 == 0 && expert_stride % 8 == 0 &&
+                        (((size_t)x | (size_t)weights) & 15) == 0;
     if (act_dtype == kFloat32)
         launch_chained(expert_rows_kernel<float>, grid, warps * 32, 0, stream, (const float*)x, x_stride, pairs_per_row,
                        chosen, (const float*)weights, expert_stride, w_stride, (float*)out, out_stride, pairs, n, k,
-                       activation);
+                       activation, 0);
     else
         launch_chained(expert_rows_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream, (const __nv_bfloat16*)x, x_stride,
                        pairs_per_row, chosen, (const __nv_bfloat16*)weights, expert_stride, w_stride, (__nv_bfloat16*)out,
-                       out_stride, pairs, n, k, activation);
+                       out_stride, pairs, n, k, activation, vectors);
     return check_launch("expert_rows");
 }
 

@@ -111,8 +111,7 @@ _SIGNATURES = {
     "celeg_head_project": [c_void_p, c_int, c_int, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_int, c_int,
                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_head_gate": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-    "celeg_moe_route": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                        c_int, c_int, c_void_p],
+    "celeg_moe_route": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "celeg_moe_group": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "celeg_moe_gather_rows": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_gemm_tcgen05_grouped": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
@@ -736,18 +735,18 @@ def moe_max_tiles(pairs: int, experts: int, tile_rows: int = MOE_TILE) -> int:
     return pairs // tile_rows + min(pairs, experts)
 
 
-def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor],
-              shared_gate_weight: Optional[torch.Tensor], chosen: torch.Tensor, weights: torch.Tensor,
-              shared_gate: Optional[torch.Tensor], tokens: int, top: int) -> None:
-    """chosen int32 [tokens, top], weights float32 [tokens, top]: the ``top`` experts with the largest
-    softmax(router h) + correction and their softmax scores divided by their sum; shared_gate float32 [tokens] =
-    sigmoid(shared_gate_weight . h). Sums in float32."""
-    _need(router, torch.float32, "router")
-    experts, width = router.shape
-    assert h.stride(-1) == 1 and h.shape[-1] == width and chosen.dtype == torch.int32 and weights.dtype == torch.float32
-    _check(library().celeg_moe_route(_ptr(h), h.stride(0), _ptr(router), _ptr(correction), _ptr(shared_gate_weight),
-                                     _ptr(chosen), _ptr(weights), _ptr(shared_gate), tokens, width, experts, top,
-                                     dtype_code(h.dtype), _stream()))
+def moe_route(logits: torch.Tensor, experts: int, correction: Optional[torch.Tensor], gate_column: Optional[int],
+              chosen: torch.Tensor, weights: torch.Tensor, shared_gate: Optional[torch.Tensor], tokens: int,
+              top: int) -> None:
+    """From router logits (float32 [tokens, >= experts], a product with float32 sums): chosen int32 [tokens, top] and
+    weights float32 [tokens, top], the ``top`` experts with the largest softmax(logits[:, :experts]) + correction and
+    their softmax scores divided by their sum; shared_gate float32 [tokens] = sigmoid(logits[:, gate_column])."""
+    _need(chosen, torch.int32, "chosen")
+    _need(weights, torch.float32, "weights")
+    assert logits.dtype == torch.float32 and logits.stride(-1) == 1 and logits.shape[-1] >= experts
+    _check(library().celeg_moe_route(_ptr(logits), logits.stride(0), _ptr(correction),
+                                     -1 if gate_column is None else gate_column, _ptr(chosen), _ptr(weights),
+                                     _ptr(shared_gate), tokens, experts, top, _stream()))
 
 
 def moe_group(chosen: torch.Tensor, tokens: int, experts: int, top: int, place_of_pair: torch.Tensor,

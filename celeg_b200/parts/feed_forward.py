@@ -72,7 +72,7 @@ class DenseFeedForward:
 @register_part("feed_forward", "moe")
 class MoeFeedForward:
     """A mixture of ``experts`` small feed-forwards down_e(act(up_e(x))) of which each token uses ``top``:
-    s = softmax(W_router x) over all experts (float32), the experts with the largest s + ``correction`` are
+    s = softmax(W_router x) over all experts (float32 sums and softmax), the experts with the largest s + ``correction`` are
     chosen, their weights are their s divided by the sum of the chosen s (+ 1e-20), and the output is the weighted
     sum of their outputs. A nested part ``shared`` (any feed-forward) runs for every token and is added, times
     sigmoid(w_shared_gate . x) when the tensor ``shared_gate`` is given.
@@ -98,9 +98,12 @@ class MoeFeedForward:
         self.activation = DenseFeedForward.ACTIVATIONS[name]
         if not 0 < self.top <= self.experts:
             raise ValueError(f"moe: top {self.top} of {self.experts} experts")
-        self.router = rt.vector(weights["router"])
+        # the router's matrix, with the shared expert's gate as one more row: one product with float32 sums gives both
+        self.gated = "shared_gate" in weights and parts.get("shared") is not None
+        rows = [weights["router"]] + ([weights["shared_gate"].reshape(1, -1)] if self.gated else [])
+        self.w_router = rt.matrix(torch.cat(rows, dim=0))
+        self.logits = rt.scratch("moe.logits", int(self.w_router.shape[0]), torch.float32)
         self.correction = rt.vector(weights["correction"]) if "correction" in weights else None
-        self.shared_gate_weight = rt.vector(weights["shared_gate"].reshape(-1)) if "shared_gate" in weights else None
         self.w_up = rt.matrix(torch.stack([weights[f"e{e}.up"] for e in range(self.experts)]))        # [E, inner, hidden]
         self.w_down = rt.matrix(torch.stack([weights[f"e{e}.down"] for e in range(self.experts)]))    # [E, hidden, inner]
         self.shared = parts.get("shared")
@@ -120,8 +123,9 @@ class MoeFeedForward:
     def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
         t, top = step.tokens, self.top
         pairs = t * top
-        gated = self.shared is not None and self.shared_gate_weight is not None
-        kernels.moe_route(x, self.router, self.correction, self.shared_gate_weight if gated else None, self.chosen,
+        gated = self.gated
+        self.rt.linear(x, self.w_router, self.logits, t)
+        kernels.moe_route(self.logits, self.experts, self.correction, self.experts if gated else None, self.chosen,
                           self.weights, self.shared_gate if gated else None, t, top)
         if self.shared is not None:
             self.shared.forward(x, self.shared_out, step)

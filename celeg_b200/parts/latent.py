@@ -92,11 +92,24 @@ class LatentAttentionMixer(PagedAttentionKernels):
         kernels.latent_prepare(q, down, self.down_norm, self.frequencies, self.magnitude, self.eps, step.positions,
                                step.token_span, table, b.k, b.page_tokens, self.qkv, t, self.heads, self.dim,
                                self.rot, self.rotary_dim, self.rank, step.error_flag)
+        library = rt.act_dtype == torch.bfloat16 and not rt.small_batch(t)
         # the query in the latent space: (U_h^T q_h) for every head, beside its rotated part
-        kernels.head_project(q, self.dim + self.rot, self.w_up_keys, True, self.qkv, self.head_dim, t, self.heads,
-                             self.rank, self.dim)
+        if library:
+            # many bfloat16 rows: one batched library product over the heads (views, nothing is copied)
+            torch.bmm(q[:t].unflatten(1, (self.heads, self.dim + self.rot))[:, :, :self.dim].transpose(0, 1),
+                      self.w_up_keys.view(self.heads, self.dim, self.rank),
+                      out=self.qkv[:t].unflatten(1, (self.heads, self.head_dim))[:, :, :self.rank].transpose(0, 1))
+        else:
+            kernels.head_project(q, self.dim + self.rot, self.w_up_keys, True, self.qkv, self.head_dim, t, self.heads,
+                                 self.rank, self.dim)
         self.attend(step, table)
         # V_h (sum p c) times the head's gate
-        kernels.head_project(self.attended, self.head_dim, self.w_up_values, False, self.values, self.vdim, t,
-                             self.heads, self.vdim, self.rank, gate=gate)
+        if library:
+            torch.bmm(self.attended[:t].unflatten(1, (self.heads, self.head_dim))[:, :, :self.rank].transpose(0, 1),
+                      self.w_up_values.view(self.heads, self.vdim, self.rank).transpose(1, 2),
+                      out=self.values[:t].unflatten(1, (self.heads, self.vdim)).transpose(0, 1))
+            kernels.head_gate(self.values, self.vdim, gate, t, self.heads)
+        else:
+            kernels.head_project(self.attended, self.head_dim, self.w_up_values, False, self.values, self.vdim, t,
+                                 self.heads, self.vdim, self.rank, gate=gate)
         rt.linear(self.values, self.w_out, out, t)

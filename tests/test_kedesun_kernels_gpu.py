@@ -242,6 +242,7 @@ def test_retention_scan_and_decoding_kernel(dim, vdim, heads):
 @pytest.mark.parametrize("experts,top,width,tokens", [(4, 1, 36, 9), (16, 3, 256, 70), (40, 8, 100, 33), (70, 70, 64, 5)])
 def test_router_chooses_by_corrected_scores(dtype, experts, top, width, tokens):
     from celeg_b200 import kernels
+    from celeg_b200.parts import Runtime
     rng = np.random.default_rng(6)
     h = rounded(rng.normal(size=(tokens, width)), dtype)
     router = rounded(rng.normal(size=(experts, width)) * 3.0 / np.sqrt(width), torch.bfloat16)
@@ -250,8 +251,12 @@ def test_router_chooses_by_corrected_scores(dtype, experts, top, width, tokens):
     chosen = torch.zeros((tokens, top), dtype=torch.int32, device="cuda")
     weights = torch.zeros((tokens, top), dtype=torch.float32, device="cuda")
     shared = torch.zeros(tokens, dtype=torch.float32, device="cuda")
-    kernels.moe_route(dev(h, dtype), dev(router, torch.float32), dev(correction, torch.float32), dev(gate_w, torch.float32),
-                      chosen, weights, shared, tokens, top)
+    # the logits as the engine makes them: one product with float32 sums, the gate's row after the experts'
+    rt = Runtime(torch.device("cuda:0"), dtype, 128, max_requests=4, max_context=128)
+    logits = torch.zeros((128, experts + 1), dtype=torch.float32, device="cuda")
+    rt.linear(dev(np.concatenate([h, np.zeros((128 - tokens, width))]), dtype), dev(np.concatenate([router, gate_w[None, :]]), dtype),
+              logits, tokens)
+    kernels.moe_route(logits, experts, dev(correction, torch.float32), experts, chosen, weights, shared, tokens, top)
     tensors = {"m.router": router, "m.correction": correction}
     want_chosen, want_weights = plain.route(tensors, "m.", {"router": {"top": top}}, h)
     logits = h @ router.T
