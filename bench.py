@@ -196,7 +196,7 @@ class KernelTimer:
              "add_dyt", "add_to_residual", "join_stream_embedding", "activation", "softcap", "recurrent_scan",
              "mlstm_gates", "delta_prepare", "gated_head_norm", "qk_whole_norm_rope_store", "recurrent_decode",
              "depth_average", "latent_prepare", "head_project", "head_gate", "moe_route", "moe_group", "moe_gather_rows",
-             "expert_product", "expert_product_tcgen05", "expert_rows", "moe_combine")
+             "expert_product", "expert_product_tcgen05", "expert_rows", "moe_combine", "retention_segmented")
 
     def __init__(self):
         self.pairs = []

@@ -507,6 +507,21 @@ static int launch_tc_persistent(const CUtensorMap& map_a, const CUtensorMap& map
     return check_launch("gemm_tcgen05 (persistent)");
 }
 
+template <int BN, int STAGES, int EPI>
+static int launch_grouped(const CUtensorMap& map_a, const CUtensorMap& map_b, const TcGemmParams& p, int max_tiles,
+                          cudaStream_t stream) {
+    constexpr size_t smem = (size_t)STAGES * (kTileM * kTileK * 2 + BN * kTileK * 2) + 1024;
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES, EPI>;
+    const cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (status != cudaSuccess) {
+        set_error("gemm_tcgen05_grouped: %s", cudaGetErrorString(status));
+        return -2;
+    }
+    dim3 grid((p.n + BN - 1) / BN, max_tiles);
+    kernel<<<grid, kGemmThreads, smem, stream>>>(map_a, map_b, p);
+    return check_launch("gemm_tcgen05_grouped");
+}
+
 }  // namespace celeg_b200
 
 using namespace celeg_b200;
@@ -573,10 +588,10 @@ CELEG_API int celeg_gemm_tcgen05(const void* a, int lda, const void* b, int ldb,
 // Grouped product: c[r, :n] = a[r, :k] * b[g(r)][:n, :k]^T, where b holds `groups` matrices of n rows one after the
 // other and the device-made table (see TcGemmParams) assigns runs of rows of a to groups in tiles of at most 128
 // rows. max_tiles bounds the table's tiles and sizes the grid; rows of a: a_rows. epilogue 0 (bfloat16) or 3.. (an
-// activation). The same kernel as the plain product with 128 x 128 tiles, two blocks per SM.
+// activation). The same kernel as the plain product's one-tile-a-block forms; wide_tiles: -1 = chosen from n, 0 / 1.
 CELEG_API int celeg_gemm_tcgen05_grouped(const void* a, int lda, int a_rows, const void* b, int ldb, int groups, void* c,
                                          int ldc, const int* table, int max_tiles, int n, int k, int epilogue,
-                                         int* error_flag, cudaStream_t stream) {
+                                         int* error_flag, int wide_tiles, cudaStream_t stream) {
     CELEG_REQUIRE(a_rows > 0 && n > 0 && k > 0 && groups > 0 && max_tiles >= 0 && table != nullptr,
                   "gemm_tcgen05_grouped: invalid sizes rows=%d n=%d k=%d groups=%d tiles=%d", a_rows, n, k, groups, max_tiles);
     CELEG_REQUIRE(k % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && lda >= k && ldb >= k,
@@ -587,26 +602,15 @@ CELEG_API int celeg_gemm_tcgen05_grouped(const void* a, int lda, int a_rows, con
                   "gemm_tcgen05_grouped: unknown epilogue %d", epilogue);
     CELEG_REQUIRE(max_tiles <= 65535, "gemm_tcgen05_grouped: %d tiles exceed one launch", max_tiles);
     if (max_tiles == 0) return 0;
+    // wide outputs: tiles of 128 x 256 (half as many passes over the rows); else 128 x 128, two blocks per SM
+    const bool wide = wide_tiles < 0 ? n >= 1024 : wide_tiles != 0;
     CUtensorMap map_a, map_b;
     if (!tensor_map_for(a, a_rows, k, lda, kTileM, &map_a)) return -3;
-    if (!tensor_map_for(b, (long long)groups * n, k, ldb, 128, &map_b)) return -3;
+    if (!tensor_map_for(b, (long long)groups * n, k, ldb, wide ? 256 : 128, &map_b)) return -3;
     TcGemmParams p{a_rows, n, k, c, ldc, error_flag, epilogue >= kTcActivation ? epilogue - kTcActivation : 0, table, n};
-    constexpr int BN = 128, STAGES = 3;
-    constexpr size_t smem = (size_t)STAGES * (kTileM * kTileK * 2 + BN * kTileK * 2) + 1024;
-    dim3 grid((n + BN - 1) / BN, max_tiles);
-    cudaError_t status;
-    if (epilogue == kTcStoreBf16) {
-        auto kernel = gemm_tcgen05_kernel<BN, STAGES, kTcStoreBf16>;
-        status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (status == cudaSuccess) kernel<<<grid, kGemmThreads, smem, stream>>>(map_a, map_b, p);
-    } else {
-        auto kernel = gemm_tcgen05_kernel<BN, STAGES, kTcActivation>;
-        status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (status == cudaSuccess) kernel<<<grid, kGemmThreads, smem, stream>>>(map_a, map_b, p);
-    }
-    if (status != cudaSuccess) {
-        set_error("gemm_tcgen05_grouped: %s", cudaGetErrorString(status));
-        return -2;
-    }
-    return check_launch("gemm_tcgen05_grouped");
+    const bool store = epilogue == kTcStoreBf16;
+    if (wide) return store ? launch_grouped<256, 4, kTcStoreBf16>(map_a, map_b, p, max_tiles, stream)
+                           : launch_grouped<256, 4, kTcActivation>(map_a, map_b, p, max_tiles, stream);
+    return store ? launch_grouped<128, 3, kTcStoreBf16>(map_a, map_b, p, max_tiles, stream)
+                 : launch_grouped<128, 3, kTcActivation>(map_a, map_b, p, max_tiles, stream);
 }

@@ -595,6 +595,104 @@ __global__ void __launch_bounds__(256) recurrent_decode_kernel(const DecodeStepP
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Retention over long spans, cut into segments. With a constant decay d the state after token t of a segment
+// that begins at token b is S_t = d^(t-b+1) S_(b-1) + L_t, L_t the state the segment's own tokens would have built
+// from zero. So the segments of all spans are scanned side by side from zero states (the scan kernel above, one
+// "span" a segment), which also gives the segment's final L and the local read-outs L_t^T q_t; the states at the
+// segments' starts follow from one another by S <- d^len S + L (a handful of steps a span, element by element);
+// and the read-outs get d^(t-b+1) S_(b-1)^T q_t added, a small product per segment. Only rounding differs
+// from the token-by-token order.
+__global__ void retention_plan_kernel(const int* span_begin, int spans, int segment, int max_segments, int* seg_begin,
+                                      int* span_first) {
+    chain_release();
+    chain_wait();
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int n = 0;
+    for (int s = 0; s < spans; ++s) {
+        span_first[s] = n;
+        for (int b = span_begin[s]; b < span_begin[s + 1] && n < max_segments; b += segment) seg_begin[n++] = b;
+    }
+    span_first[spans] = n;
+    for (int i = n; i <= max_segments; ++i) seg_begin[i] = span_begin[spans];      // (segments beyond the last are empty)
+}
+
+// one thread a state element: the state at every segment's start, and the span's state after its last token
+__global__ void retention_carry_kernel(float* state, long long slot_stride, const int* span_slot, const int* span_first,
+                                       const int* seg_begin, const float* local, float* carried, const float* decay,
+                                       int elements, int head_elements) {
+    chain_release();
+    chain_wait();
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= elements) return;
+    const int span = blockIdx.y;
+    float* cell = state + (long long)span_slot[span] * slot_stride + e;
+    const float d = decay[e / head_elements];
+    float s = *cell;
+    for (int seg = span_first[span]; seg < span_first[span + 1]; ++seg) {
+        carried[(size_t)seg * elements + e] = s;
+        s = fmaf(powf(d, (float)(seg_begin[seg + 1] - seg_begin[seg])), s, local[(size_t)seg * elements + e]);
+    }
+    *cell = s;
+}
+
+// out[t, head, :] += d^(t - b + 1) (carried[segment of t][head]^T q_t): 64 tokens x 64 columns a block, FFMA
+__global__ void __launch_bounds__(256) retention_add_carried_kernel(const float* q, int q_stride, const float* carried,
+                                                                    const int* seg_begin, const float* decay, float* out,
+                                                                    int heads, int dim, int vdim, int pieces) {
+    __shared__ float qs[16][64 + 4];
+    __shared__ float ss[16][64 + 4];
+    chain_release();
+    chain_wait();
+    const int seg = blockIdx.z / pieces, piece = blockIdx.z % pieces;
+    const int head = blockIdx.y, col0 = blockIdx.x * 64;
+    const int begin = seg_begin[seg], end = seg_begin[seg + 1];
+    const int t0 = begin + piece * 64;
+    if (t0 >= end) return;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const float* state = carried + ((size_t)seg * heads + head) * dim * vdim;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < dim; k0 += 16) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = threadIdx.x + i * 256;
+            const int r = idx >> 4, kk = idx & 15;            // queries: 16 k of a token are neighbours
+            qs[kk][r] = (t0 + r < end && k0 + kk < dim) ? q[(size_t)(t0 + r) * q_stride + (size_t)head * dim + k0 + kk] : 0.0f;
+            const int c = idx & 63, kr = idx >> 6;            // state rows: 64 columns of a k are neighbours
+            ss[kr][c] = (col0 + c < vdim && k0 + kr < dim) ? state[(size_t)(k0 + kr) * vdim + col0 + c] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = qs[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = ss[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    const float d = decay[head];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int t = t0 + ty * 4 + i;
+        if (t >= end) continue;
+        const float factor = powf(d, (float)(t - begin + 1));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = col0 + tx * 4 + j;
+            if (c < vdim) {
+                float* cell = out + (size_t)t * heads * vdim + (size_t)head * vdim + c;
+                *cell = fmaf(factor, acc[i][j], *cell);
+            }
+        }
+    }
+}
+
 template <int MODE>
 static int launch_scan(const ScanParams& p, int spans, cudaStream_t stream) {
     int lanes = 1;
@@ -753,4 +851,51 @@ CELEG_API int celeg_recurrent_decode(int mode, const float* proj, int stride, in
     else
         launch_chained(recurrent_decode_kernel<kScanMlstm, __nv_bfloat16>, grid, kDecodeStepThreads, smem, stream, p);
     return check_launch("recurrent_decode");
+}
+
+// Retention over the step's spans in segments of `segment` tokens (a multiple of 64). Scratch: floats
+// [2 * max_segments * heads * dim * vdim] (the segments' own states, then the states at their starts), ints
+// [max_segments + spans + 2] (segment starts, the spans' first segments), with max_segments >= tokens / segment +
+// spans; identity: the numbers 0 .. max_segments - 1. decay: [heads]. Same result as mode 2 of celeg_recurrent_scan
+// but for rounding.
+CELEG_API int celeg_retention_segmented(const float* q, int q_stride, const float* k, int k_stride, const float* v,
+                                        int v_stride, const float* decay, float* out, float* state, long long slot_stride,
+                                        const int* span_begin, const int* span_slot, int spans, int tokens, int heads,
+                                        int dim, int vdim, float q_scale, int segment, int max_segments,
+                                        float* float_scratch, int* int_scratch, const int* identity,
+                                        cudaStream_t stream) {
+    CELEG_REQUIRE(spans >= 0 && tokens >= 0 && heads > 0 && dim > 0 && vdim > 0 && segment >= 64 && segment % 64 == 0,
+                  "retention_segmented: invalid sizes spans=%d tokens=%d heads=%d dim=%d vdim=%d segment=%d", spans, tokens,
+                  heads, dim, vdim, segment);
+    CELEG_REQUIRE(dim <= kScanMaxDim, "retention_segmented: a key size of %d exceeds %d", dim, kScanMaxDim);
+    CELEG_REQUIRE(max_segments >= tokens / segment + spans && max_segments <= 65535 && spans <= 65535 && heads <= 65535,
+                  "retention_segmented: %d segments do not hold %d tokens in %d spans (or exceed one launch)", max_segments,
+                  tokens, spans);
+    if (spans == 0 || tokens == 0) return 0;
+    const long long elements = (long long)heads * dim * vdim;
+    float* local = float_scratch;
+    float* carried = float_scratch + (size_t)max_segments * elements;
+    int* seg_begin = int_scratch;                          // [max_segments + 1]
+    int* span_first = int_scratch + max_segments + 1;      // [spans + 1]
+    cudaMemsetAsync(local, 0, (size_t)max_segments * elements * sizeof(float), stream);
+    launch_chained(retention_plan_kernel, 1, 32, 0, stream, span_begin, spans, segment, max_segments, seg_begin, span_first);
+    int status = check_launch("retention_plan");
+    if (status != 0) return status;
+    const int vector_copies = dim % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && (((size_t)q | (size_t)k) & 15) == 0;
+    const ScanParams p = {q, k, v, q_stride, k_stride, v_stride, decay, out, local, elements, seg_begin, identity,
+                          heads, heads, dim, vdim, q_scale, vector_copies};
+    status = launch_scan<kScanRetention>(p, max_segments, stream);
+    if (status != 0) return status;
+    dim3 carry_grid((unsigned)((elements + 255) / 256), spans);
+    retention_carry_kernel<<<carry_grid, 256, 0, stream>>>(state, slot_stride, span_slot, span_first, seg_begin, local,
+                                                            carried, decay, (int)elements, dim * vdim);
+    status = check_launch("retention_carry");
+    if (status != 0) return status;
+    const int pieces = segment / 64;
+    dim3 add_grid((vdim + 63) / 64, heads, max_segments * pieces);
+    CELEG_REQUIRE((long long)max_segments * pieces <= 65535, "retention_segmented: %d segments of %d pieces exceed one launch",
+                  max_segments, pieces);
+    retention_add_carried_kernel<<<add_grid, 256, 0, stream>>>(q, q_stride, carried, seg_begin, decay, out, heads, dim, vdim,
+                                                                pieces);
+    return check_launch("retention_add_carried");
 }

@@ -103,6 +103,9 @@ _SIGNATURES = {
                             c_int, c_float, c_void_p],
     "celeg_gated_head_norm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_int,
                               c_int, c_void_p],
+    "celeg_retention_segmented": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong,
+                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+                                  c_void_p, c_void_p, c_void_p],
     "celeg_depth_average": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
                             c_float, c_int, c_int, c_int, c_void_p],
     "celeg_latent_prepare": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p,
@@ -115,7 +118,7 @@ _SIGNATURES = {
     "celeg_moe_group": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "celeg_moe_gather_rows": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_gemm_tcgen05_grouped": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
-                                   c_int, c_int, c_void_p, c_void_p],
+                                   c_int, c_int, c_void_p, c_int, c_void_p],
     "celeg_expert_product": [c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_int,
                              c_int, c_int, c_int, c_int, c_void_p],
     "celeg_expert_rows": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int,
@@ -607,6 +610,27 @@ def recurrent_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                                           _ptr(span_slot), spans, heads, kv_heads, dim, vdim, q_scale, _stream()))
 
 
+def retention_segmented(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, out: torch.Tensor,
+                        state: torch.Tensor, slot_stride: int, span_begin: torch.Tensor, span_slot: torch.Tensor, spans: int,
+                        tokens: int, heads: int, dim: int, vdim: int, q_scale: float, segment: int, max_segments: int,
+                        float_scratch: torch.Tensor, int_scratch: torch.Tensor, identity: torch.Tensor) -> None:
+    """The retention (mode SCAN_RETENTION of :func:`recurrent_scan`) with every span cut into segments of ``segment``
+    tokens that are scanned side by side, the states at their starts carried from one to the next, and the carried
+    share added to the read-outs (csrc/recurrent_scan.cu). Scratch: float32 [2 * max_segments * heads * dim * vdim],
+    int32 [max_segments + spans + 2], ``identity`` = arange(max_segments) int32."""
+    for tensor in (q, k, v, decay, out, state, float_scratch):
+        assert tensor.dtype == torch.float32 and tensor.stride(-1) == 1
+    assert out.is_contiguous() and out.shape[1] == heads * vdim and decay.shape == (heads,)
+    assert max_segments >= tokens // segment + spans and identity.numel() >= max_segments
+    assert float_scratch.numel() >= 2 * max_segments * heads * dim * vdim and int_scratch.numel() >= max_segments + spans + 2
+    _check(library().celeg_retention_segmented(_ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(decay),
+                                               _ptr(out), _ptr(state), slot_stride, _ptr(span_begin), _ptr(span_slot), spans,
+                                               tokens, heads, dim, vdim, q_scale, segment, max_segments,
+                                               _ptr(float_scratch), _ptr(int_scratch), _ptr(identity), _stream()))
+    global LAUNCHES
+    LAUNCHES += 4          # the plan, the scan, the carried states, their share of the read-outs (and a memset)
+
+
 def recurrent_decode(mode: int, proj: torch.Tensor, offsets: Tuple[int, int, int, int, int, int],
                      conv_kernel: Optional[torch.Tensor], carried: Optional[torch.Tensor], taps: int, channels: int,
                      bias0: torch.Tensor, bias1: torch.Tensor, cap: float, norm_weight: torch.Tensor,
@@ -774,15 +798,16 @@ def expert_product_tcgen05_supported(x: torch.Tensor, weights: torch.Tensor) -> 
 
 
 def expert_product_tcgen05(x: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, table: torch.Tensor,
-                           max_tiles: int, activation: int, error_flag: torch.Tensor) -> None:
+                           max_tiles: int, activation: int, error_flag: torch.Tensor, wide_tiles: int = -1) -> None:
     """out[place] = act(x[place] @ weights[expert of the place]^T) on tcgen05 over a tile table of 128-row tiles;
-    ``x`` holds the rows in the order of their places. ``activation``: a code of ACT_* or -1."""
+    ``x`` holds the rows in the order of their places. ``activation``: a code of ACT_* or -1. ``wide_tiles``: output
+    tiles of 256 columns (1) or 128 (0); -1: chosen from the shape."""
     _, n, k = weights.shape
     assert out.dtype == torch.bfloat16 and out.stride(-1) == 1 and out.shape[-1] == n and x.shape[-1] == k
     _check(library().celeg_gemm_tcgen05_grouped(_ptr(x), x.stride(0), x.shape[0], _ptr(weights), weights.stride(1),
                                                 weights.shape[0], _ptr(out), out.stride(0), _ptr(table), max_tiles, n, k,
                                                 TC_STORE if activation < 0 else TC_ACTIVATION + activation,
-                                                _ptr(error_flag), _stream()))
+                                                _ptr(error_flag), wide_tiles, _stream()))
 
 
 def expert_product(x: torch.Tensor, source: Optional[torch.Tensor], weights: torch.Tensor, out: torch.Tensor,

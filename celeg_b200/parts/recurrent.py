@@ -219,6 +219,16 @@ class RetentionMixer:
         self.projected = rt.scratch("recurrent.proj", self.proj_width, torch.float32)
         self.read = rt.scratch("recurrent.read", self.v_width, torch.float32)
         self.gated = rt.scratch("recurrent.gated", self.v_width)
+        # long prompts: segments of SEGMENT tokens scanned side by side (the decay is a constant, so a segment's
+        # state and read-outs from a zero state are corrected afterwards by what was carried into it)
+        self.max_segments = rt.max_tokens // self.SEGMENT + rt.max_requests + 16
+        elements = self.heads * self.dim * self.vdim
+        self.segment_states = rt.flat_scratch("retention.segments", 2 * self.max_segments * elements, torch.float32)
+        self.segment_plan = rt.flat_scratch("retention.plan", 2 * self.max_segments + 8, torch.int32, zero=True)
+        self.segment_numbers = torch.arange(self.max_segments, dtype=torch.int32, device=rt.device)
+
+    SEGMENT = 128               # tokens a segment
+    SEGMENTED_FROM = 384        # steps of at least this many tokens are scanned in segments
 
     def cache_need(self):
         return StateNeed(elements=self.heads * self.dim * self.vdim)
@@ -246,9 +256,15 @@ class RetentionMixer:
         k = rows[:, width:2 * width]
         v = rows[:, 2 * width:2 * width + self.v_width]
         gate = rows[:, 2 * width + self.v_width:]
-        kernels.recurrent_scan(kernels.SCAN_RETENTION, q, k, v, self.decay, self.read, b.state, b.slot_stride,
-                               step.span_begin, step.span_slot, step.spans, self.heads, self.heads, self.dim,
-                               self.vdim, self.dim ** -0.5)
+        segments = t // self.SEGMENT + step.spans
+        if t >= self.SEGMENTED_FROM and segments <= self.max_segments and segments + step.spans + 2 <= self.segment_plan.numel():
+            kernels.retention_segmented(q, k, v, self.decay, self.read, b.state, b.slot_stride, step.span_begin,
+                                        step.span_slot, step.spans, t, self.heads, self.dim, self.vdim, self.dim ** -0.5,
+                                        self.SEGMENT, segments, self.segment_states, self.segment_plan, self.segment_numbers)
+        else:
+            kernels.recurrent_scan(kernels.SCAN_RETENTION, q, k, v, self.decay, self.read, b.state, b.slot_stride,
+                                   step.span_begin, step.span_slot, step.spans, self.heads, self.heads, self.dim,
+                                   self.vdim, self.dim ** -0.5)
         kernels.gated_head_norm(self.read, gate, None, False, self.gated, t, self.heads, self.vdim, self.eps,
                                 kernels.GATE_SILU)
         rt.linear(self.gated, self.w_out, out, t)

@@ -180,6 +180,22 @@ def test_pages_and_slots_are_used_again(models, dtype):
     assert loaded.manager.free_slots == 2
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["mixed", "wide"])
+def test_long_portions_beside_short_ones(models, name, dtype):
+    """Portions of hundreds of tokens (the retention scans them in segments, the experts' pairs are grouped) beside
+    single tokens and short portions of other requests, from states and caches that earlier portions left."""
+    folder, raw, tensors = models[name]
+    long_one, short_one, other = tokens_of(raw["vocab"], 1100, 31), tokens_of(raw["vocab"], 140, 32), tokens_of(raw["vocab"], 400, 33)
+    want = {"a": plain.logits(raw, tensors, long_one), "b": plain.logits(raw, tensors, short_one), "c": plain.logits(raw, tensors, other)}
+    loaded = load(folder, dtype, cache_tokens=2048, max_batched_tokens=1024, max_context=2048)
+    steps = [[("b", short_one[:1]), ("a", long_one[:449])], [("b", short_one[1:2]), ("a", long_one[449:450]), ("c", other[:385])],
+             [("b", short_one[2:131]), ("a", long_one[450:1027]), ("c", other[385:])], [("b", short_one[131:]), ("a", long_one[1027:])]]
+    got = run_steps(loaded, steps)
+    for key in want:
+        check(got[key], want[key], dtype, f"{name} request {key} in long portions", routed=True)
+
+
 def test_long_decoding_from_the_first_token(models):
     folder, raw, tensors = models["mixed"]
     tokens = tokens_of(raw["vocab"], 200, 7)

@@ -238,6 +238,38 @@ def test_retention_scan_and_decoding_kernel(dim, vdim, heads):
         states.update(before)
 
 
+@pytest.mark.parametrize("dim,vdim,heads,segment", [(16, 24, 2, 64), (64, 128, 3, 128), (40, 7, 1, 128), (136, 70, 2, 192)])
+def test_retention_in_segments_equals_the_token_by_token_scan(dim, vdim, heads, segment):
+    """Spans of unequal length (shorter than a segment, exactly one, one token more, several) from states that earlier
+    tokens left: read-outs and final states as the plain scan's, and the slots' other floats untouched."""
+    from celeg_b200 import kernels
+    rng = np.random.default_rng(8)
+    lengths = [segment * 3 + 17, 1, segment, segment + 1, 5, 2 * segment]
+    slots = [4, 0, 2, 5, 1, 3]
+    tokens, spans = sum(lengths), len(lengths)
+    decay = dev(np.array(([1.0, 0.9, 0.99951171875] * 2)[:heads], dtype=np.float32))
+    elements = heads * dim * vdim
+    stride = (elements + 3) // 4 * 4 + 12
+    state0 = dev(rng.normal(size=(7, stride)).astype(np.float32))
+    proj = dev(rng.normal(size=(tokens, heads * (2 * dim + vdim))).astype(np.float32))
+    q, k, v = proj[:, :heads * dim], proj[:, heads * dim:2 * heads * dim], proj[:, 2 * heads * dim:]
+    span_begin = dev(np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32))
+    span_slot = dev(np.array(slots, dtype=np.int32))
+    want_state, want = state0.clone(), torch.zeros((tokens, heads * vdim), dtype=torch.float32, device="cuda")
+    kernels.recurrent_scan(kernels.SCAN_RETENTION, q, k, v, decay, want, want_state, stride, span_begin, span_slot, spans,
+                           heads, heads, dim, vdim, dim ** -0.5)
+    segments = tokens // segment + spans
+    got_state, got = state0.clone(), torch.full((tokens, heads * vdim), 9.0, dtype=torch.float32, device="cuda")
+    floats = torch.full((2 * segments * elements,), 5.0, dtype=torch.float32, device="cuda")
+    ints = torch.zeros(segments + spans + 2, dtype=torch.int32, device="cuda")
+    kernels.retention_segmented(q, k, v, decay, got, got_state, stride, span_begin, span_slot, spans, tokens, heads, dim, vdim,
+                                dim ** -0.5, segment, segments, floats, ints, torch.arange(segments, dtype=torch.int32, device="cuda"))
+    scale = float(want.abs().max())
+    assert float((got - want).abs().max()) <= 2e-5 * scale
+    assert float((got_state - want_state).abs().max()) <= 2e-5 * float(want_state.abs().max())
+    assert torch.equal(got_state[:, elements:], state0[:, elements:]) and torch.equal(got_state[6], state0[6])
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("experts,top,width,tokens", [(4, 1, 36, 9), (16, 3, 256, 70), (40, 8, 100, 33), (70, 70, 64, 5)])
 def test_router_chooses_by_corrected_scores(dtype, experts, top, width, tokens):
