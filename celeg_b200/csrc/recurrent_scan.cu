@@ -603,6 +603,130 @@ __global__ void __launch_bounds__(256) recurrent_decode_kernel(const DecodeStepP
 // segments' starts follow from one another by S <- d^len S + L (a handful of steps a span, element by element);
 // and the read-outs get d^(t-b+1) S_(b-1)^T q_t added, a small product per segment. Only rounding differs
 // from the token-by-token order.
+// The segments' scan, built for throughput instead of a short chain per token (many segments run side by side, so
+// no single one is waited for): a lane holds 64 consecutive elements of a column of S (the whole column up to a key
+// size of 64; L = 2 or 4 lanes a column beyond), reads a token's key and query as 16-byte broadcasts from shared
+// memory, and k.q is formed once per token for all columns. Per element and token that is a third of the
+// instructions of the kernel above, which spreads a column over eight lanes to keep ONE long span's chain short.
+template <int L>
+__global__ void __launch_bounds__(kScanThreads) retention_wide_scan_kernel(const ScanParams p) {
+    constexpr int kE = 64;
+    constexpr int kColsWarp = 32 / L;
+    constexpr int kCols = kScanWarps * kColsWarp;
+    constexpr int kDimPad = kE * L;
+    constexpr int kTile = L > 2 ? 8 : 16;
+    __shared__ __align__(16) float k_s[2][kTile][kDimPad];
+    __shared__ __align__(16) float q_s[2][kTile][kDimPad];
+    __shared__ float v_s[2][kTile][kCols];
+    __shared__ float kq_s[2][kTile];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int sub = lane % L, col_in = warp * kColsWarp + lane / L;
+    const int head = blockIdx.y, span = blockIdx.z;
+    const int col = blockIdx.x * kCols + col_in;
+    const bool col_ok = col < p.vdim;
+    const int dim = p.dim, vdim = p.vdim;
+    const int t_begin = p.span_begin[span], t_end = p.span_begin[span + 1];
+    if (t_end <= t_begin) return;
+    for (int i = tid; i < 2 * kTile * kDimPad; i += kScanThreads) {      // keys beyond the head's size stay zero
+        (&k_s[0][0][0])[i] = 0.0f;
+        (&q_s[0][0][0])[i] = 0.0f;
+    }
+    for (int i = tid; i < 2 * kTile * kCols; i += kScanThreads) (&v_s[0][0][0])[i] = 0.0f;
+    __syncthreads();
+    float* s_head = p.state + (long long)p.span_slot[span] * p.slot_stride + (size_t)head * dim * vdim;
+    const float decay = p.gates[head];
+    float s[kE];
+#pragma unroll
+    for (int r = 0; r < kE; ++r) {
+        const int e = sub * kE + r;
+        s[r] = (col_ok && e < dim) ? s_head[(size_t)e * vdim + col] : 0.0f;
+    }
+    const float* k_base = p.k + (size_t)head * dim;
+    const float* q_base = p.q + (size_t)head * dim;
+    auto issue = [&](int t0, int stage) {
+        const int count = min(kTile, t_end - t0);
+        if (p.vector_copies) {
+            const int quads = dim >> 2;
+            for (int i = tid; i < count * quads; i += kScanThreads) {
+                const int tt = i / quads, e = (i - tt * quads) << 2;
+                cp_async_16(&k_s[stage][tt][e], k_base + (size_t)(t0 + tt) * p.k_stride + e);
+                cp_async_16(&q_s[stage][tt][e], q_base + (size_t)(t0 + tt) * p.q_stride + e);
+            }
+        } else {
+            for (int i = tid; i < count * dim; i += kScanThreads) {
+                const int tt = i / dim, e = i - tt * dim;
+                cp_async_4(&k_s[stage][tt][e], k_base + (size_t)(t0 + tt) * p.k_stride + e);
+                cp_async_4(&q_s[stage][tt][e], q_base + (size_t)(t0 + tt) * p.q_stride + e);
+            }
+        }
+        for (int i = tid; i < count * kCols; i += kScanThreads) {
+            const int tt = i / kCols, c = i % kCols;
+            const int gc = blockIdx.x * kCols + c;
+            if (gc < vdim) cp_async_4(&v_s[stage][tt][c], p.v + (size_t)(t0 + tt) * p.v_stride + (size_t)head * vdim + gc);
+        }
+        cp_async_commit_group();
+    };
+    issue(t_begin, 0);
+    int stage = 0;
+    for (int t0 = t_begin; t0 < t_end; t0 += kTile, stage ^= 1) {
+        if (t0 + kTile < t_end) {
+            issue(t0 + kTile, stage ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();                                // every thread's copies of this stage have landed
+        const int count = min(kTile, t_end - t0);
+        for (int tt = warp; tt < count; tt += kScanWarps) {            // k.q of the tile's tokens, a warp a token
+            float sum = 0.0f;
+            for (int e = lane; e < kDimPad; e += 32) sum = fmaf(k_s[stage][tt][e], q_s[stage][tt][e], sum);
+            sum = warp_sum(sum);
+            if (lane == 0) kq_s[stage][tt] = sum * p.q_scale;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < count; ++tt) {
+            const float vj = v_s[stage][tt][col_in];
+            const float vs = vj * p.q_scale;
+            const float4* kp = reinterpret_cast<const float4*>(&k_s[stage][tt][sub * kE]);
+            const float4* qp = reinterpret_cast<const float4*>(&q_s[stage][tt][sub * kE]);
+            float sq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int r4 = 0; r4 < kE / 4; ++r4) {
+                const float4 kv = kp[r4], qv = qp[r4];
+                sq[0] = fmaf(s[4 * r4], qv.x, sq[0]);
+                sq[1] = fmaf(s[4 * r4 + 1], qv.y, sq[1]);
+                sq[2] = fmaf(s[4 * r4 + 2], qv.z, sq[2]);
+                sq[3] = fmaf(s[4 * r4 + 3], qv.w, sq[3]);
+                s[4 * r4] = fmaf(kv.x, vs, decay * s[4 * r4]);
+                s[4 * r4 + 1] = fmaf(kv.y, vs, decay * s[4 * r4 + 1]);
+                s[4 * r4 + 2] = fmaf(kv.z, vs, decay * s[4 * r4 + 2]);
+                s[4 * r4 + 3] = fmaf(kv.w, vs, decay * s[4 * r4 + 3]);
+            }
+            float d_sq = (sq[0] + sq[1]) + (sq[2] + sq[3]);
+#pragma unroll
+            for (int offset = 1; offset < L; offset <<= 1) d_sq += __shfl_xor_sync(0xffffffffu, d_sq, offset);
+            if (sub == 0 && col_ok)
+                p.out[(size_t)(t0 + tt) * p.heads * vdim + (size_t)head * vdim + col] = fmaf(decay, d_sq, vj * kq_s[stage][tt]);
+        }
+        __syncthreads();                                // the stage is free for the tile after the next
+    }
+#pragma unroll
+    for (int r = 0; r < kE; ++r) {
+        const int e = sub * kE + r;
+        if (col_ok && e < dim) s_head[(size_t)e * vdim + col] = s[r];
+    }
+}
+
+static int launch_wide_scan(const ScanParams& p, int spans, cudaStream_t stream) {
+    const int lanes = p.dim <= 64 ? 1 : p.dim <= 128 ? 2 : 4;
+    const int cols = kScanWarps * (32 / lanes);
+    dim3 grid((p.vdim + cols - 1) / cols, p.heads, spans);
+    if (lanes == 1) retention_wide_scan_kernel<1><<<grid, kScanThreads, 0, stream>>>(p);
+    else if (lanes == 2) retention_wide_scan_kernel<2><<<grid, kScanThreads, 0, stream>>>(p);
+    else retention_wide_scan_kernel<4><<<grid, kScanThreads, 0, stream>>>(p);
+    return check_launch("retention_wide_scan");
+}
+
 __global__ void retention_plan_kernel(const int* span_begin, int spans, int segment, int max_segments, int* seg_begin,
                                       int* span_first) {
     chain_release();
@@ -884,7 +1008,7 @@ CELEG_API int celeg_retention_segmented(const float* q, int q_stride, const floa
     const int vector_copies = dim % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && (((size_t)q | (size_t)k) & 15) == 0;
     const ScanParams p = {q, k, v, q_stride, k_stride, v_stride, decay, out, local, elements, seg_begin, identity,
                           heads, heads, dim, vdim, q_scale, vector_copies};
-    status = launch_scan<kScanRetention>(p, max_segments, stream);
+    status = launch_wide_scan(p, max_segments, stream);
     if (status != 0) return status;
     dim3 carry_grid((unsigned)((elements + 255) / 256), spans);
     retention_carry_kernel<<<carry_grid, 256, 0, stream>>>(state, slot_stride, span_slot, span_first, seg_begin, local,
