@@ -167,14 +167,14 @@ def test_pages_and_slots_are_used_again(models, dtype):
     folder, raw, tensors = models["mixed"]
     loaded = load(folder, dtype, max_requests=2, cache_tokens=160)
     lengths = [75, 60, 31, 80, 17, 66]
-    for round_ in range(3):
-        pair = {f"x{2 * round_}": tokens_of(raw["vocab"], lengths[2 * round_], 20 + round_),
-                f"y{2 * round_}": tokens_of(raw["vocab"], lengths[2 * round_ + 1], 30 + round_)}
+    for turn in range(3):
+        pair = {f"x{2 * turn}": tokens_of(raw["vocab"], lengths[2 * turn], 20 + turn),
+                f"y{2 * turn}": tokens_of(raw["vocab"], lengths[2 * turn + 1], 30 + turn)}
         (a, ta), (b, tb) = pair.items()
         steps = [[(a, ta[:20]), (b, tb[:3])], [(a, ta[20:21]), (b, tb[3:])], [(a, ta[21:])]]
         got = run_steps(loaded, steps)
         for key, tokens in pair.items():
-            check(got[key], plain.logits(raw, tensors, tokens), dtype, f"round {round_} request {key}", routed=True)
+            check(got[key], plain.logits(raw, tensors, tokens), dtype, f"turn {turn} request {key}", routed=True)
             loaded.step.end(key)
         loaded.manager.check_invariants()
     assert loaded.manager.free_slots == 2
