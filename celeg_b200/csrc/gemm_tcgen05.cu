@@ -230,9 +230,27 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const unsigned smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int k_tiles = (p.k + kTileK - 1) / kTileK;
-    const int m_tiles = (p.m + kTileM - 1) / kTileM;
+    const int m_tiles = p.table != nullptr ? p.table[0] : (p.m + kTileM - 1) / kTileM;
     const int n_tiles = (p.n + kOutColumns - 1) / kOutColumns;
     const int tiles = m_tiles * n_tiles;
+    // Where a tile lies: first row of A and C, first column of C, first row of B, and how many of its 128 rows count.
+    // Plain product: consecutive tiles walk down M and share their B tile. Grouped product (a table of row tiles,
+    // see TcGemmParams): consecutive tiles walk along N, so blocks that run together share the rows and stream
+    // one group's matrix.
+    auto origin = [&](int tile, int& m0, int& n0, int& b_row0, int& rows_here) {
+        if (p.table != nullptr) {
+            const int* entry = p.table + 4 + 3 * (tile / n_tiles);
+            n0 = (tile % n_tiles) * kOutColumns;
+            m0 = entry[1];
+            rows_here = entry[2];
+            b_row0 = entry[0] * p.group_rows + n0;
+        } else {
+            m0 = (tile % m_tiles) * kTileM;
+            n0 = (tile / m_tiles) * kOutColumns;
+            rows_here = p.m - m0;
+            b_row0 = n0;
+        }
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -256,8 +274,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         if (lane == 0) {
             int it = 0;                                     // k-tiles issued so far, over all tiles
             for (int tile = blockIdx.x; tile < tiles && !abort_flag; tile += gridDim.x) {
-                const int m0 = (tile % m_tiles) * kTileM;
-                const int n0 = (tile / m_tiles) * kOutColumns;
+                int m0, n0, b_row0, rows_here;
+                origin(tile, m0, n0, b_row0, rows_here);
                 for (int kt = 0; kt < k_tiles; ++kt, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(smem_u32(&empty_bar[s]), ((it / STAGES) - 1) & 1)) {
@@ -274,7 +292,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                         tma_load_2d(b_dst, &map_b, bar, kt * kTileK, n0);
                         tma_load_2d(b_dst + kBytesB / 2, &map_b, bar, kt * kTileK, p.n + n0);
                     } else {
-                        tma_load_2d(b_dst, &map_b, bar, kt * kTileK, n0);
+                        tma_load_2d(b_dst, &map_b, bar, kt * kTileK, b_row0);
                     }
                 }
             }
@@ -330,9 +348,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                 break;
             }
             tcgen05_fence_after();
-            const int m0 = (tile % m_tiles) * kTileM;
-            const int n0 = (tile / m_tiles) * kOutColumns;
+            int m0, n0, b_row0, rows_here;
+            origin(tile, m0, n0, b_row0, rows_here);
             const int row = m0 + quarter * 32 + lane;
+            const bool row_ok = quarter * 32 + lane < rows_here;
             const unsigned lane_base = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN);
 #pragma unroll 1
             for (int c0 = 0; c0 < kOutColumns; c0 += 32) {
@@ -353,7 +372,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                     for (int i = 0; i < 32; ++i)
                         v[i] = activate(__bfloat162float(__float2bfloat16_rn(v[i])), p.activation);
                 }
-                if (row < p.m) {
+                if (row_ok) {
                     const int col = n0 + c0;
                     if (EPI == kTcStoreF32) {
                         float* dst = reinterpret_cast<float*>(p.c) + (size_t)row * p.ldc + col;
@@ -486,7 +505,7 @@ static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_b, const T
 
 template <int EPI>
 static int launch_tc_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const TcGemmParams& p,
-                                cudaStream_t stream) {
+                                cudaStream_t stream, int grouped_row_tiles = 0) {
     constexpr size_t smem = (size_t)kPersistentStages * (kTileM * kTileK * 2 + kPersistentBN * kTileK * 2) + 1024;
     auto kernel = gemm_tcgen05_persistent_kernel<EPI>;
     const cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -502,7 +521,9 @@ static int launch_tc_persistent(const CUtensorMap& map_a, const CUtensorMap& map
         if (sms <= 0) sms = 148;
     }
     constexpr int out_columns = EPI == kTcSwiGlu ? kPersistentBN / 2 : kPersistentBN;
-    const int tiles = ((p.m + kTileM - 1) / kTileM) * ((p.n + out_columns - 1) / out_columns);
+    // (a grouped product's row tiles are counted on the device: blocks for the most there can be, the rest idle)
+    const int row_tiles = grouped_row_tiles > 0 ? grouped_row_tiles : (p.m + kTileM - 1) / kTileM;
+    const int tiles = row_tiles * ((p.n + out_columns - 1) / out_columns);
     kernel<<<tiles < sms ? tiles : sms, kPersistentThreads, smem, stream>>>(map_a, map_b, p);
     return check_launch("gemm_tcgen05 (persistent)");
 }
@@ -609,6 +630,12 @@ CELEG_API int celeg_gemm_tcgen05_grouped(const void* a, int lda, int a_rows, con
     if (!tensor_map_for(b, (long long)groups * n, k, ldb, wide ? 256 : 128, &map_b)) return -3;
     TcGemmParams p{a_rows, n, k, c, ldc, error_flag, epilogue >= kTcActivation ? epilogue - kTcActivation : 0, table, n};
     const bool store = epilogue == kTcStoreBf16;
+    if (wide_tiles < 0 && max_tiles * ((n + 255) / 256) >= 148) {
+        // many tiles: the persistent form (128 x 256 tiles, two accumulators, the epilogue under the next tile's MMAs)
+        if (!tensor_map_for(b, (long long)groups * n, k, ldb, 256, &map_b)) return -3;
+        return store ? launch_tc_persistent<kTcStoreBf16>(map_a, map_b, p, stream, max_tiles)
+                     : launch_tc_persistent<kTcActivation>(map_a, map_b, p, stream, max_tiles);
+    }
     if (wide) return store ? launch_grouped<256, 4, kTcStoreBf16>(map_a, map_b, p, max_tiles, stream)
                            : launch_grouped<256, 4, kTcActivation>(map_a, map_b, p, max_tiles, stream);
     return store ? launch_grouped<128, 3, kTcStoreBf16>(map_a, map_b, p, max_tiles, stream)

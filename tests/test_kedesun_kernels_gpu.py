@@ -308,7 +308,8 @@ def test_router_chooses_by_corrected_scores(dtype, experts, top, width, tokens):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("experts,top,width,inner,tokens", [(4, 2, 40, 24, 7), (16, 3, 256, 64, 200), (5, 5, 36, 20, 70),
-                                                             (40, 1, 64, 72, 130), (3, 2, 100, 33, 90), (8, 2, 512, 384, 700)])
+                                                             (40, 1, 64, 72, 130), (3, 2, 100, 33, 90), (8, 2, 512, 384, 700),
+                                                             (32, 4, 512, 768, 2048)])
 def test_experts_products_grouped_and_row_by_row(dtype, experts, top, width, inner, tokens):
     """The forms of the experts' two products (tile by tile over the pairs grouped by expert, on tcgen05 where the
     shapes allow, and row by row) against the plain mixture, and against each other."""
